@@ -11,9 +11,11 @@ their own, so a windowed group can give pages back while a full group keeps
 them.  The reference keeps one KV geometry per model and refuses a mix
 (src/model/runtime.hpp:531-533); here the mix is the point.
 
-Storage of one member: `[num_pages, 2, kv_heads, page_size, head_dim]`, plane 0
+Storage of one member: `[num_pages, planes, kv_heads, page_size, head_dim]`, plane 0
 keys and plane 1 values, so one (page, head) run of keys is contiguous
-(`page_size * head_dim` elements), which is what a bulk copy wants.
+(`page_size * head_dim` elements), which is what a bulk copy wants.  A mixer that
+keeps one vector per token (a latent from which keys and values are made when
+they are read) asks for `planes=1`; pages, block tables and windows are the same.
 
 State: `StateSlots` hands out slot ids; each state entry owns
 `[num_slots, *shape]`.  A request takes one slot for its life.  A mixer must
@@ -34,6 +36,7 @@ class KVSpec:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every key is kept
+    planes: int = 2                   # 2: keys and values; 1: one vector per token (a latent that keys and values are made from)
 
 
 @dataclass(frozen=True)
@@ -94,7 +97,7 @@ class CacheGroup:
         self.storage = None               # torch tensor [len(members), num_pages, 2, G, page, D] once allocated
 
     def bytes_per_page(self, element_size: int) -> int:
-        return len(self.members) * 2 * self.spec.kv_heads * self.page_size * self.spec.head_dim * element_size
+        return len(self.members) * self.spec.planes * self.spec.kv_heads * self.page_size * self.spec.head_dim * element_size
 
 
 class RequestCache:
@@ -228,7 +231,7 @@ class CacheManager:
         for g in self.groups:
             s = g.spec
             # Zero-filled: a kernel may load (and mask) slots of a page that were never written.
-            g.storage = torch.zeros((len(g.members), g.pool.num_pages, 2, s.kv_heads, g.page_size, s.head_dim),
+            g.storage = torch.zeros((len(g.members), g.pool.num_pages, s.planes, s.kv_heads, g.page_size, s.head_dim),
                                     dtype=self.kv_dtype, device=self.device)
         for e in self.state_entries:
             s = self.entry_specs[e]
@@ -244,7 +247,8 @@ class CacheManager:
                 if storage is None:
                     continue
                 if gi >= 0:
-                    self.views.set_kv(e, gi, storage)
+                    if self.entry_specs[e].planes == 2:      # one-plane entries are read by their own mixer's kernels only
+                        self.views.set_kv(e, gi, storage)
                 else:
                     self.views.set_state(e, storage)
 

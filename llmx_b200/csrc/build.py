@@ -44,6 +44,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
+    "recurrence": ["recurrence.cu"],          # matrix-state recurrences (decayed linear attention, gated delta rule) and the short convolution
+    "latent_attention": ["latent_attention.cu"],   # attention over a cache of latents
     "selftest": ["selftest.cu"],              # the bounded wait made to run out on purpose (tests)
     "runtime": ["runtime/runtime.cpp", "runtime/engine.cpp", "runtime/loader.cpp"],       # host code: the parts' forward passes (no kernels of its own)
 }

@@ -394,3 +394,210 @@ LLMX_EXPORT int llmx_swiglu(const float* gu, void* act, int out_dtype, int rows,
     else launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float*)act, total, width);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Embedding with a factor: x[r, :] = table[ids[r], :] * scale, the product made in 32-bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_scaled_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                                    int width, int table_rows, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    float* dst = x + (size_t)r * width;
+    if (id < 0 || id >= table_rows) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    const T* src = table + (size_t)id * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
+}
+
+LLMX_EXPORT int llmx_embed_scaled(const void* table, int table_dtype, const int* ids, float* x, int rows, int width,
+                                  int table_rows, float scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (table_dtype == LLMX_BF16)
+        launch_kernel(embed_scaled_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, x, width, table_rows, scale);
+    else
+        launch_kernel(embed_scaled_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)table, ids, x, width, table_rows, scale);
+    return launch_status();
+}
+
+// x[i] *= s over a flat float buffer (a model whose logits carry a factor).
+__global__ void scale_kernel(float* __restrict__ x, long long n, float s) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+
+LLMX_EXPORT int llmx_scale(float* x, long long n, float s, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    launch_kernel(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, s);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm with a weight and no bias: m = mean x; v = mean (x - m)^2; y_i = (x_i - m) / sqrt(v + eps) * w_i.
+// Two passes over the row's values (kept in registers when the row fits, else read again): the variance is the
+// mean of squared deviations, not a difference of means.  `row_index` as in RMSNorm.
+// ---------------------------------------------------------------------------
+constexpr int LN_MAX = 16;   // values a thread keeps (rows up to 16 * 256 wide); wider rows are read three times
+
+template <typename OutT>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
+                                 const int* __restrict__ row_index, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
+    OutT* dst = y + (size_t)r * width;
+    const float inv_n = 1.0f / (float)width;
+    if (width <= LN_MAX * (int)blockDim.x) {
+        float v[LN_MAX];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LN_MAX; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            v[k] = i < width ? src[i] : 0.0f;
+            s += v[k];
+        }
+        const float mean = block_sum(s, scratch) * inv_n;
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LN_MAX; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            const float d = i < width ? v[k] - mean : 0.0f;
+            v[k] = d;
+            q = fmaf(d, d, q);
+        }
+        const float rr = 1.0f / sqrtf(block_sum(q, scratch) * inv_n + eps);
+#pragma unroll
+        for (int k = 0; k < LN_MAX; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < width) dst[i] = from_float<OutT>(v[k] * rr * w[i]);
+        }
+        return;
+    }
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) s += src[i];
+    const float mean = block_sum(s, scratch) * inv_n;
+    float q = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = src[i] - mean;
+        q = fmaf(d, d, q);
+    }
+    const float rr = 1.0f / sqrtf(block_sum(q, scratch) * inv_n + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<OutT>((src[i] - mean) * rr * w[i]);
+}
+
+LLMX_EXPORT int llmx_layernorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
+                               int width, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    // The block width follows the row width alone, so a row's sums have one order whatever the batch.
+    int threads = (width + LN_MAX - 1) / LN_MAX;
+    threads = (threads + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : threads > 256 ? 256 : threads;
+    if (out_dtype == LLMX_BF16)
+        launch_kernel(layernorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, width, eps);
+    else
+        launch_kernel(layernorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)y, row_index, width, eps);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Clamped gated unit: g = min(gate, limit); u = clamp(up, -limit, limit); act = g * sigmoid(alpha * g) * (u + 1).
+// `gu` holds a row's gate values then its up values ([rows, 2 * width]); 32-bit arithmetic.
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, OutT* __restrict__ act, long long total, int width,
+                                   float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / width;
+    const int c = (int)(i % width);
+    const float g = fminf(gu[r * 2 * width + c], limit);
+    const float u = fminf(fmaxf(gu[r * 2 * width + width + c], -limit), limit);
+    act[i] = from_float<OutT>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
+LLMX_EXPORT int llmx_clamped_glu(const float* gu, void* act, int out_dtype, int rows, int width, float limit, float alpha,
+                                 cudaStream_t stream) {
+    const long long total = (long long)rows * width;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == LLMX_BF16) launch_kernel(clamped_glu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, gu, (__nv_bfloat16*)act, total, width, limit, alpha);
+    else launch_kernel(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float*)act, total, width, limit, alpha);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// In-place activation of a column range of a float matrix: x[r, c0 .. c0 + n) = silu(x).  (A mixer whose
+// projections pass an activation before a recurrence reads them.)
+// ---------------------------------------------------------------------------
+__global__ void silu_columns_kernel(float* __restrict__ x, int stride, int c0, int n, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float* p = x + (i / n) * stride + c0 + (i % n);
+    const float v = *p;
+    *p = v / (1.0f + expf(-v));
+}
+
+LLMX_EXPORT int llmx_silu_columns(float* x, int rows, int stride, int c0, int n, cudaStream_t stream) {
+    const long long total = (long long)rows * n;
+    if (total <= 0) return 0;
+    if (c0 < 0 || c0 + n > stride) return LLMX_ERR_BAD_ARGUMENT;
+    launch_kernel(silu_columns_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, stride, c0, n, total);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm over groups of a row, times a gate: for group j of `group` values,
+//   y = o / sqrt(mean_group(o^2) + eps) * w[(j * group + i) % w_len] * act(gate),  act = sigmoid (0) or silu (1).
+// One group is the whole row (a norm over all heads together, weight as long as the row) or one head (weight as
+// long as a head and shared by the heads).  `gate` has its own row stride (it lies inside a wider product's output).
+// One block per (row, group); the block width follows the group width alone.
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride,
+                                     const float* __restrict__ w, int w_len, OutT* __restrict__ y, int groups, int group,
+                                     float eps, int gate_kind) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x, j = blockIdx.y;
+    const size_t base = ((size_t)r * groups + j) * group;
+    const float* src = o + base;
+    const float* gsrc = gate + (size_t)r * gate_stride + (size_t)j * group;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) s = fmaf(src[i], src[i], s);
+    const float rr = 1.0f / sqrtf(block_sum(s, scratch) / (float)group + eps);
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const float g = gsrc[i];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        const float a = gate_kind == 0 ? sg : g * sg;
+        y[base + i] = from_float<OutT>(src[i] * rr * w[(j * group + i) % w_len] * a);
+    }
+}
+
+LLMX_EXPORT int llmx_gated_rmsnorm(const float* o, const float* gate, int gate_stride, const float* w, int w_len, void* y,
+                                   int out_dtype, int rows, int groups, int group, float eps, int gate_kind,
+                                   cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (groups <= 0 || group <= 0 || w_len <= 0 || groups > 65535 || (gate_kind != 0 && gate_kind != 1)) return LLMX_ERR_BAD_ARGUMENT;
+    int threads = (group + 3) / 4;
+    threads = (threads + 31) / 32 * 32;
+    threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
+    if (out_dtype == LLMX_BF16)
+        launch_kernel(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (__nv_bfloat16*)y, groups, group, eps, gate_kind);
+    else
+        launch_kernel(gated_rmsnorm_kernel<float>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (float*)y, groups, group, eps, gate_kind);
+    return launch_status();
+}

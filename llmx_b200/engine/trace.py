@@ -91,5 +91,5 @@ def main(argv=None) -> int:
                                    device=int(args.device.split(":")[1]) if ":" in args.device else 0)
         return replay_native(native, sys.stdin, args.out, sys.stdout)
     engine = Engine.from_dir(args.model, EngineOptions(dtype=args.dtype, kv_tokens=kv_tokens, page_size=args.page_size,
-                                                       max_requests=16, device=args.device))
+                                                       max_requests=4, device=args.device))
     return replay(engine, sys.stdin, args.out, sys.stdout)

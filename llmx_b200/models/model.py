@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from .. import runtime
-from ..parts.base import NativeHandle, Part, PartPlan, Precision, StepBatch, StepShape
+from ..parts.base import NativeHandle, Part, PartPlan, Precision, StepBatch, StepShape, tensor_name
 from ..parts.embedding import LogitsHead, TokenEmbedding
 from ..weights.loader import check_tensors, stored
 from ..weights.spec import TensorSpec
@@ -143,7 +143,7 @@ class Model:
         out: Dict[str, TensorSpec] = {}
         for prefix, part in self._parts():
             if part is self.head:
-                out.update({prefix + r: s for r, s in part.tensor_specs().items()})
+                out.update({tensor_name(prefix, r): s for r, s in part.tensor_specs().items()})
             else:
                 out.update(part.all_tensor_specs(prefix))
         return out
@@ -161,7 +161,7 @@ class Model:
 
         for prefix, part in self._parts():
             if part is self.head:
-                mine = {r: fetch(prefix + r, s) for r, s in part.tensor_specs().items()}
+                mine = {r: fetch(tensor_name(prefix, r), s) for r, s in part.tensor_specs().items()}
                 part.load(mine, precision)
             else:
                 part.load_all(fetch, prefix, precision)

@@ -94,6 +94,19 @@ _SIGNATURES = {
     ("rowwise", "llmx_head_norm_rope_kv"): [_p, _i, _i, _i, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, _p, _i,
                                             _i, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_swiglu"): [_p, _p, _i, _i, _i, _p],
+    ("rowwise", "llmx_embed_scaled"): [_p, _i, _p, _p, _i, _i, _i, _f, _p],
+    ("rowwise", "llmx_scale"): [_p, ctypes.c_longlong, _f, _p],
+    ("rowwise", "llmx_layernorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p],
+    ("rowwise", "llmx_clamped_glu"): [_p, _p, _i, _i, _i, _f, _f, _p],
+    ("rowwise", "llmx_silu_columns"): [_p, _i, _i, _i, _i, _p],
+    ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
+    ("recurrence", "llmx_linear_recurrence"): [_p, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, ctypes.c_longlong, _p, _p, _p, _p,
+                                               _p, _p, _i, _i, _i, _i, _i, _p],
+    ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p,
+                                          ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
+    ("latent_attention", "llmx_latent_write"): [_p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
+    ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
+                                                    _i, _i, _i, _i, _i, _f, _p],
     ("gemm_plain", "llmx_gemm_plain"): [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p],
     ("attention_plain", "llmx_attention_plain"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
 }
@@ -282,4 +295,180 @@ def attention_plain(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row
         _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
         block_tables.shape[1], rows, heads, kv_heads, head_dim, cache.shape[3], int(window or 0), float(scale),
         _stream()), "attention_plain")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Row-wise kernels of models with a centred norm, factors on embedding and logits, and a clamped gated unit.
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float) -> torch.Tensor:
+    """out[r, :] = table[ids[r], :] * scale in float32."""
+    _cuda(table, ids, out)
+    rows, width = out.shape
+    _need(ids.dtype == torch.int32 and ids.numel() == rows, "embed: ids must be int32, one per output row")
+    _need(out.dtype == torch.float32 and table.dim() == 2 and table.shape[1] == width, "embed: shapes do not fit")
+    _check(_fn("rowwise", "llmx_embed_scaled")(_ptr(table), _code(table), _ptr(ids), _ptr(out), rows, width, table.shape[0],
+                                               float(scale), _stream()), "embed_scaled")
+    return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place; x float32."""
+    _cuda(x)
+    _need(x.dtype == torch.float32, "scale: a float32 tensor")
+    _check(_fn("rowwise", "llmx_scale")(_ptr(x), x.numel(), float(factor), _stream()), "scale")
+    return x
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = (x - mean) / sqrt(var + eps) * weight over row (row_index[i] or i); x float32, out float32 or bfloat16."""
+    _cuda(x, weight, out, row_index)
+    rows, width = out.shape
+    _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "layernorm: input and weight must be float32")
+    _need(x.dim() == 2 and x.shape[1] == width and weight.numel() == width, "layernorm: widths do not fit")
+    if row_index is None:
+        _need(x.shape[0] >= rows, "layernorm: fewer input rows than output rows")
+    else:
+        _need(row_index.dtype == torch.int32 and row_index.numel() == rows, "layernorm: row_index must be int32 per row")
+    _check(_fn("rowwise", "llmx_layernorm")(_ptr(x), _ptr(weight), _ptr(out), _code(out), _ptr(row_index), rows, width,
+                                            float(eps), _stream()), "layernorm")
+    return out
+
+
+def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out = g sigmoid(alpha g) (u + 1), g = min(gu[:, :F], limit), u = clamp(gu[:, F:], -limit, limit); gu float32 [rows, 2F]."""
+    _cuda(gu, out)
+    rows, width = out.shape
+    _need(gu.dtype == torch.float32 and tuple(gu.shape) == (rows, 2 * width), "clamped_glu: shapes do not fit")
+    _check(_fn("rowwise", "llmx_clamped_glu")(_ptr(gu), _ptr(out), _code(out), rows, width, float(limit), float(alpha),
+                                              _stream()), "clamped_glu")
+    return out
+
+
+def silu_columns_(x: torch.Tensor, first: int, count: int) -> torch.Tensor:
+    """x[:, first:first + count] = silu(...) in place; x float32 [rows, width]."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and 0 <= first and first + count <= x.shape[1], "silu_columns: range does not fit")
+    _check(_fn("rowwise", "llmx_silu_columns")(_ptr(x), x.shape[0], x.shape[1], int(first), int(count), _stream()), "silu_columns")
+    return x
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group: int, gate_kind: str,
+                  out: torch.Tensor) -> torch.Tensor:
+    """out = o / sqrt(mean over each group of `group` values of o^2 + eps) * weight * act(gate); act sigmoid or silu.
+    o float32 [rows, width] contiguous; gate float32 [rows, width], a view whose rows may be strided; weight float32 of
+    the row's width, or of one group's width and shared by the groups."""
+    _need(o.is_cuda and gate.is_cuda and weight.is_cuda and out.is_cuda, "kernel arguments must be CUDA tensors (there is no CPU path)")
+    rows, width = o.shape
+    _need(o.is_contiguous() and out.is_contiguous() and weight.is_contiguous(), "gated_rmsnorm: contiguous input, weight and output")
+    _need(o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32, "gated_rmsnorm: float32 inputs")
+    _need(tuple(out.shape) == (rows, width) and tuple(gate.shape) == (rows, width) and gate.stride(1) == 1, "gated_rmsnorm: shapes do not fit")
+    _need(group > 0 and width % group == 0 and weight.numel() in (group, width), "gated_rmsnorm: the group must divide the row; weight of a group or of the row")
+    _need(gate_kind in ("sigmoid", "silu"), "gated_rmsnorm: gate must be sigmoid or silu")
+    _check(_fn("rowwise", "llmx_gated_rmsnorm")(_ptr(o), _ptr(gate), gate.stride(0) if rows > 1 else width, _ptr(weight),
+                                                weight.numel(), _ptr(out), _code(out), rows, width // group, group,
+                                                float(eps), 0 if gate_kind == "sigmoid" else 1, _stream()), "gated_rmsnorm")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Matrix-state recurrences.
+def _strided_rows(t: torch.Tensor, what: str) -> int:
+    _need(t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what}: float32 rows, contiguous within a row")
+    return t.stride(0) if t.shape[0] > 1 else t.shape[1]
+
+
+def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
+                      heads: int, qk_heads: int, key_dim: int, value_dim: int, decay: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per (request, head): S <- a S + k u^T, o = S^T q over the step's rows in order, S [D, V] float32 carried in the
+    request's state slot.  With `decay` [heads]: a = decay_h, u = v.  With `gate`, `beta` [rows, heads] (views):
+    a = gate, u = beta (v - a S^T k), the gated delta rule.  q, k [rows, qk_heads * D], v [rows, heads * V]: float32
+    views whose rows may be strided.  state [slots, floats]: the recurrence's values first, [H][V][D].
+    `step`: the StepBatch (row ranges, histories and slots are read on the device)."""
+    rows = q.shape[0]
+    qs, ks, vs = _strided_rows(q, "recurrence q"), _strided_rows(k, "recurrence k"), _strided_rows(v, "recurrence v")
+    _need(q.shape[1] == qk_heads * key_dim and k.shape[1] == qk_heads * key_dim and v.shape[1] == heads * value_dim
+          and k.shape[0] == rows and v.shape[0] == rows, "recurrence: q, k, v shapes do not fit")
+    _cuda(state, out, decay)
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] >= heads * key_dim * value_dim, "recurrence: state slots too small")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (rows, heads * value_dim), "recurrence: output shape does not fit")
+    gs = 0
+    if gate is not None:
+        _need(beta is not None and decay is None, "recurrence: the delta rule takes gate and beta and no constant decay")
+        gs = _strided_rows(gate, "recurrence gate")
+        _need(_strided_rows(beta, "recurrence beta") == gs and tuple(gate.shape) == (rows, heads) and tuple(beta.shape) == (rows, heads),
+              "recurrence: gate and beta must be views of one matrix, [rows, heads]")
+    else:
+        _need(decay is not None and decay.dtype == torch.float32 and decay.numel() == heads, "recurrence: decay float32 [heads]")
+    _check(_fn("recurrence", "llmx_linear_recurrence")(
+        _ptr(q), _ptr(k), _ptr(v), qs, ks, vs, _ptr(decay), _ptr(gate), _ptr(beta), gs, _ptr(state), state.shape[1],
+        _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out),
+        _ptr(out), step.requests, heads, qk_heads, key_dim, value_dim, _stream()), "linear_recurrence")
+    return out
+
+
+def conv_prepare(proj: torch.Tensor, channels: int, q_channels: int, k_channels: int, taps_w: torch.Tensor,
+                 ready: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, b_off: int, a_off: int,
+                 gates: torch.Tensor, heads: int, key_dim: int, q_factor: float, state: torch.Tensor, conv_off: int,
+                 step) -> None:
+    """The short causal convolution, silu, unit q/k heads and the gates of a delta-rule mixer (csrc/recurrence.cu).
+    The request's slot read and the slot written must differ (a step reads one and writes its spare)."""
+    _cuda(proj, taps_w, ready, a_log, dt_bias, gates, state)
+    rows = proj.shape[0]
+    taps = taps_w.shape[1]
+    _need(proj.dtype == torch.float32 and proj.dim() == 2 and proj.shape[1] >= channels, "conv_prepare: projections float32 [rows, >= channels]")
+    _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (channels, taps), "conv_prepare: taps float32 [channels, taps]")
+    _need(ready.dtype == torch.float32 and tuple(ready.shape) == (rows, channels), "conv_prepare: output shape does not fit")
+    _need(gates.dtype == torch.float32 and tuple(gates.shape) == (rows, 2 * heads), "conv_prepare: gates float32 [rows, 2 heads]")
+    _need(a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == heads and dt_bias.numel() == heads,
+          "conv_prepare: A_log and dt_bias float32 [heads]")
+    _need(max(b_off, a_off) + heads <= proj.shape[1], "conv_prepare: gate columns outside the projections")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and conv_off + (taps - 1) * channels <= state.shape[1],
+          "conv_prepare: state slots too small")
+    _check(_fn("recurrence", "llmx_conv_prepare")(
+        _ptr(proj), proj.shape[1], channels, q_channels, k_channels, _ptr(taps_w), taps, _ptr(ready), _ptr(a_log), _ptr(dt_bias),
+        int(b_off), int(a_off), _ptr(gates), heads, key_dim, float(q_factor), _ptr(state), state.shape[1], int(conv_off),
+        _ptr(step.row_request), _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots),
+        _ptr(step.state_slots_out), rows, step.requests, _stream()), "conv_prepare")
+
+
+# ---------------------------------------------------------------------------
+# Attention over a cache of latents.
+def latent_write(dkv: torch.Tensor, weight: torch.Tensor, eps: float, freq: torch.Tensor, positions: torch.Tensor,
+                 slots: torch.Tensor, cache: torch.Tensor, latent: int, rot: int) -> None:
+    """cache[slot] = [rmsnorm(dkv[:, :latent]) * weight ; rotate(dkv[:, latent:latent + rot])]; cache [pages, 1, 1, page, latent + rot]."""
+    _cuda(dkv, weight, freq, positions, slots, cache)
+    rows = dkv.shape[0]
+    _need(dkv.dtype == torch.float32 and dkv.dim() == 2 and dkv.shape[1] == latent + rot, "latent_write: down projection float32 [rows, latent + rot]")
+    _need(weight.dtype == torch.float32 and weight.numel() == latent and freq.dtype == torch.float32 and 2 * freq.numel() <= rot,
+          "latent_write: weight [latent], frequencies [<= rot / 2]")
+    _need(cache.shape[-1] == latent + rot, "latent_write: cache rows do not fit")
+    _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= rows and slots.numel() >= rows,
+          "latent_write: positions and slots must be int32 per row")
+    _check(_fn("latent_attention", "llmx_latent_write")(_ptr(dkv), dkv.shape[1], _ptr(weight), float(eps), _ptr(freq), freq.numel(),
+                                                        _ptr(positions), _ptr(slots), _ptr(cache), _code(cache), rows, latent, rot,
+                                                        _stream()), "latent_write")
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,
+                     freq: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
+                     heads: int, key_dim: int, rot: int, value_dim: int, latent: int, page_size: int,
+                     window: Optional[int], scale: float) -> torch.Tensor:
+    """Softmax attention of query heads [key_dim unrotated ; rot rotated] over cached [latent ; rotated key part] rows, the
+    keys and values of a head being linear maps of the latent (csrc/latent_attention.cu).  q float32 [rows, heads *
+    (key_dim + rot)]; w_uk [heads * key_dim, latent], w_uv [heads * value_dim, latent] and out [rows, heads * value_dim]
+    of one type."""
+    _cuda(q, cache, w_uk, w_uv, out, freq, row_request, positions, block_tables)
+    rows = q.shape[0]
+    _need(q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot), "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
+    _need(tuple(w_uk.shape) == (heads * key_dim, latent) and tuple(w_uv.shape) == (heads * value_dim, latent)
+          and w_uk.dtype == w_uv.dtype == out.dtype, "latent_attention: key and value maps do not fit")
+    _need(tuple(out.shape) == (rows, heads * value_dim) and cache.shape[-1] == latent + rot, "latent_attention: output or cache rows do not fit")
+    for t in (row_request, positions, block_tables):
+        _need(t.dtype == torch.int32, "latent_attention: metadata must be int32")
+    _check(_fn("latent_attention", "llmx_latent_attention")(
+        _ptr(q), q.shape[1], _ptr(cache), _code(cache), _ptr(w_uk), _ptr(w_uv), _code(w_uk), _ptr(out), _ptr(freq), freq.numel(),
+        _ptr(row_request), _ptr(positions), _ptr(block_tables), block_tables.shape[1], rows, heads, key_dim, rot, value_dim,
+        latent, page_size, int(window or 0), float(scale), _stream()), "latent_attention")
     return out

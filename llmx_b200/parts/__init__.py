@@ -1,12 +1,16 @@
 """Parts a model is put together from."""
 from .base import GroupView, Part, Precision, StepBatch
 from .linear import Linear
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 from .attention import Attention
-from .mlp import GatedMLP
-from .block import PreNormBlock
+from .mlp import ClampedGLU, GatedMLP
+from .block import ParallelBlock, PreNormBlock
+from .linear_attention import DecayedLinearAttention
+from .delta_rule import GatedDeltaRule
+from .latent_attention import LatentAttention
 from .embedding import LogitsHead, TokenEmbedding
 
 __all__ = ["GroupView", "Part", "Precision", "StepBatch", "Linear", "RMSNorm", "NoPositionEncoding",
-           "RotaryEmbedding", "Attention", "GatedMLP", "PreNormBlock", "LogitsHead", "TokenEmbedding"]
+           "RotaryEmbedding", "Attention", "GatedMLP", "PreNormBlock", "LogitsHead", "TokenEmbedding", "LayerNorm", "ClampedGLU",
+           "ParallelBlock", "DecayedLinearAttention", "GatedDeltaRule", "LatentAttention"]

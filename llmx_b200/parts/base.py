@@ -100,6 +100,13 @@ class PartPlan:
         pass
 
 
+def tensor_name(prefix: str, role: str) -> str:
+    """The name of a part's tensor: the part's prefix and the tensor's role.  A part with one tensor may give it the
+    empty role; the tensor is then named by the prefix alone, without its trailing dot ("final.norm", not
+    "final.norm.weight")."""
+    return prefix + role if role else prefix.rstrip(".")
+
+
 class Part:
     """Base of every part: tensors by role, loaded once.
 
@@ -133,7 +140,7 @@ class Part:
 
     # -- composition ---------------------------------------------------------
     def all_tensor_specs(self, prefix: str = "") -> Dict[str, TensorSpec]:
-        out = {prefix + role: spec for role, spec in self.tensor_specs().items()}
+        out = {tensor_name(prefix, role): spec for role, spec in self.tensor_specs().items()}
         for name, child in self.children().items():
             out.update(child.all_tensor_specs(f"{prefix}{name}."))
         return out
@@ -142,7 +149,7 @@ class Part:
         """`fetch(name, spec)` returns the stored tensor on the device, or None for an absent optional one."""
         mine = {}
         for role, spec in self.tensor_specs().items():
-            t = fetch(prefix + role, spec)
+            t = fetch(tensor_name(prefix, role), spec)
             if t is not None:
                 mine[role] = t
         self.load(mine, precision)

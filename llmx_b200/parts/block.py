@@ -73,3 +73,33 @@ class PreNormBlock(Part):
         self.mixer.forward(h, step, cache_entry, x, write_cache)
         h = self.ffn_norm.forward(x, zero=_cleared(self.ffn, rows, x.device, step))
         self.ffn.forward(h, step, x)
+
+
+class ParallelBlock(Part):
+    """x += mixer(norm(x)) + ffn(norm(x)): one norm, and both parts read its output and add into the float32
+    residual.  `ffn` may be None (a layer with a mixer only).  `names`: the prefixes of the three parts' tensors."""
+
+    def __init__(self, norm: Part, mixer: Part, ffn: Optional[Part], names=("norm", "mixer", "mlp")):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+        self.names = tuple(names)
+
+    def children(self) -> Dict[str, Part]:
+        out = {self.names[0]: self.norm, self.names[1]: self.mixer}
+        if self.ffn is not None:
+            out[self.names[2]] = self.ffn
+        return out
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, x: torch.Tensor, step: StepBatch, cache_entry: Optional[int], write_cache: bool = True) -> None:
+        """x: the float32 residual stream [rows, hidden], updated in place."""
+        rows = x.shape[0]
+        cleared = [_cleared(p, rows, x.device, step) for p in (self.mixer, self.ffn) if p is not None]
+        h = self.norm.forward(x)
+        for z in cleared:                 # two buffers may want clearing and a norm clears one in passing: both here
+            if z is not None:
+                z.zero_()
+        self.mixer.forward(h, step, cache_entry, x, write_cache)
+        if self.ffn is not None:
+            self.ffn.forward(h, step, x)

@@ -13,23 +13,27 @@ from .linear import Linear, bare_step
 
 
 class TokenEmbedding(Part):
-    """x[r, :] = table[ids[r], :] widened to 32-bit (src/model/arch/blocks.hpp:95-97)."""
+    """x[r, :] = table[ids[r], :] widened to 32-bit (src/model/arch/blocks.hpp:95-97), times `scale` when the
+    architecture has a factor on its embedding (the product is made in 32-bit).  `role`: the table's tensor role."""
 
-    def __init__(self, vocab: int, hidden: int):
+    def __init__(self, vocab: int, hidden: int, scale: float = 1.0, role: str = "weight"):
         self.vocab, self.hidden = int(vocab), int(hidden)
+        self.scale, self.role = float(scale), role
         self.table: Optional[torch.Tensor] = None
         self._native: Optional[NativeHandle] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.vocab, self.hidden), "table")}
+        return {self.role: TensorSpec((self.vocab, self.hidden), "table")}
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
-        self.table = tensors["weight"].to(precision.act).contiguous()
+        self.table = tensors[self.role].to(precision.act).contiguous()
         self._native = None
 
     @property
-    def native(self) -> int:
+    def native(self):
+        if self.scale != 1.0:
+            return None               # the runtime's embedding has no factor: the kernel with one is called from here
         if self._native is None:
             runtime.need("rowwise")
             self._native = NativeHandle(runtime.lib().llmx_embedding_create(self.table.data_ptr(), runtime.code(self.table.dtype),
@@ -40,6 +44,9 @@ class TokenEmbedding(Part):
         if not (ids.is_cuda and ids.dtype is torch.int32 and ids.is_contiguous()):
             raise runtime.KernelError("embed: ids must be int32 on the device")
         x = torch.empty((ids.numel(), self.hidden), dtype=torch.float32, device=ids.device)
+        if self.scale != 1.0:
+            from .. import ops
+            return ops.embed_scaled(self.table, ids, x, self.scale)
         s = bare_step(ids.device)
         runtime.check(runtime.lib().llmx_embedding_forward(self.native, ctypes.byref(s), ids.data_ptr(), x.data_ptr(), ids.numel()),
                       "embed")
@@ -53,19 +60,22 @@ class LogitsHead(Part):
     is given, the embedding's table (the reference's alias, src/model/runtime.hpp:46-53).
     """
 
-    def __init__(self, norm: Part, vocab: int, hidden: int, tied_to: Optional[TokenEmbedding] = None):
+    def __init__(self, norm: Part, vocab: int, hidden: int, tied_to: Optional[TokenEmbedding] = None, scale: float = 1.0,
+                 role: str = "weight"):
+        """`scale`: a factor on the logits (applied to the float32 product); `role`: the weight's tensor role."""
         self.norm, self.vocab, self.hidden, self.tied_to = norm, int(vocab), int(hidden), tied_to
+        self.scale, self.role = float(scale), role
         self.linear: Optional[Linear] = None
         self._native: Optional[NativeHandle] = None
         self._native_tried = False
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {} if self.tied_to is not None else {"weight": TensorSpec((self.vocab, self.hidden))}
+        return {} if self.tied_to is not None else {self.role: TensorSpec((self.vocab, self.hidden))}
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
         if self.tied_to is None:
-            self.linear = Linear(tensors["weight"], precision)
+            self.linear = Linear(tensors[self.role], precision)
         self._native, self._native_tried = None, False
 
     def bind_tied(self) -> None:
@@ -78,7 +88,7 @@ class LogitsHead(Part):
     def native(self):
         if not self._native_tried:
             self._native_tried = True
-            norm = self.norm.native
+            norm = self.norm.native if self.scale == 1.0 else None
             if norm:
                 d = self.linear.desc()
                 self._native = NativeHandle(runtime.lib().llmx_head_create(norm, ctypes.byref(d)), keep=(self.norm, self.linear.weight))
@@ -86,4 +96,8 @@ class LogitsHead(Part):
 
     def forward(self, x: torch.Tensor, logit_rows: torch.Tensor) -> torch.Tensor:
         h = self.norm.forward(x, row_index=logit_rows)
-        return self.linear(h)
+        logits = self.linear(h)
+        if self.scale != 1.0:
+            from .. import ops
+            ops.scale_(logits, self.scale)
+        return logits

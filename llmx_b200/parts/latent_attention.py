@@ -1,0 +1,83 @@
+"""Latent attention: queries, keys and values through low-rank latents, and a cache of the latents alone.
+
+For the rows of a step, with H heads, D unrotated and R rotated query/key values per head, V value values per head,
+a query latent of `q_rank` and a key/value latent of C = `kv_rank` values:
+    cq = RMSNorm(h Wdq^T) * w_dq;   q = cq Wuq^T, per head [D unrotated | R rotated]
+    [c_raw | r_raw] = h Wdkv^T (C + R values);   c = RMSNorm(c_raw) * w_dkv;   r = rotate(r_raw) (one part for all heads)
+    per head: k = [Wuk_h c | r],  v = Wuv_h c,   s = (q_plain . Wuk_h c + rotate(q_rot) . r) * scale
+    o = softmax over the keys lo..p (lo = 0, or p - window + 1 under a sliding window) of s, times v
+    residual += o Wo^T
+Only [c | r] is cached, one vector per token (a cache entry of one plane).  The rotation pairs neighbours
+(2i, 2i + 1) of the first `rot_dims` values of the rotated part by the angle p * base^(-2i / rot_dims).  The kernels
+(csrc/latent_attention.cu) never make keys or values of cached tokens: the query goes through Wuk once, the weighted
+sum of latents through Wuv once.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from .. import ops, runtime
+from ..cache.manager import KVSpec
+from ..weights.spec import TensorSpec
+from .base import Part, Precision, StepBatch
+from .linear import Linear
+
+
+class LatentAttention(Part):
+    def __init__(self, hidden: int, heads: int, key_dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
+                 scale: float, rot_base: float, rot_dims: int, norm_eps: float, window: Optional[int] = None):
+        if rot_dims % 2 or rot_dims > rot_dim or rot_dims < 0:
+            raise ValueError("latent attention: the rotated width must be even and at most the rotated part's width")
+        self.hidden, self.heads, self.key_dim, self.rot_dim, self.value_dim = int(hidden), int(heads), int(key_dim), int(rot_dim), int(value_dim)
+        self.q_rank, self.kv_rank, self.scale = int(q_rank), int(kv_rank), float(scale)
+        self.rot_base, self.rot_dims, self.norm_eps = float(rot_base), int(rot_dims), float(norm_eps)
+        self.window = int(window) if window else None
+        self.q_width = self.heads * (self.key_dim + self.rot_dim)
+        self.v_width = self.heads * self.value_dim
+        self.freq: Optional[torch.Tensor] = None
+
+    def cache_spec(self):
+        return KVSpec(1, self.kv_rank + self.rot_dim, self.window, planes=1)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        E, C, R = self.hidden, self.kv_rank, self.rot_dim
+        return {"dq": TensorSpec((self.q_rank, E)), "dq.norm": TensorSpec((self.q_rank,), "vector", init="one_plus_normal", std=0.01),
+                "uq": TensorSpec((self.q_width, self.q_rank)),
+                "dkv": TensorSpec((C + R, E)), "dkv.norm": TensorSpec((C,), "vector", init="one_plus_normal", std=0.01),
+                "uk": TensorSpec((self.heads * self.key_dim, C)), "uv": TensorSpec((self.v_width, C)),
+                "o": TensorSpec((E, self.v_width))}
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        t = tensors
+        self.dq, self.uq, self.dkv, self.o = (Linear(t[n], precision) for n in ("dq", "uq", "dkv", "o"))
+        self.dq_norm = t["dq.norm"].to(torch.float32).contiguous()
+        self.dkv_norm = t["dkv.norm"].to(torch.float32).contiguous()
+        self.w_uk = t["uk"].to(precision.act).contiguous()
+        self.w_uv = t["uv"].to(precision.act).contiguous()
+        # f_i = base^(-2i / dims) in double precision, rounded once; the angle is the float product with the position.
+        i = np.arange(self.rot_dims // 2, dtype=np.float64)
+        freq = np.power(np.float64(self.rot_base), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
+        self.freq = torch.from_numpy(freq).to(self.w_uk.device)
+
+    def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
+                write_cache: bool = True) -> None:
+        rows = h.shape[0]
+        if not (h.is_cuda and h.is_contiguous() and h.dtype is self.precision.act and tuple(h.shape) == (rows, self.hidden)
+                and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
+            raise runtime.KernelError("latent attention: rows of the path's type and the mixer's width, a float32 residual")
+        group, cache = step.kv(cache_entry)
+        if write_cache:
+            ops.latent_write(self.dkv(h), self.dkv_norm, self.norm_eps, self.freq, step.positions, group.slots, cache,
+                             self.kv_rank, self.rot_dim)
+        cq = torch.empty((rows, self.q_rank), dtype=self.precision.act, device=h.device)
+        ops.rmsnorm(self.dq(h), self.dq_norm, self.norm_eps, cq)
+        q = self.uq(cq)
+        o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
+        ops.latent_attention(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions, group.block_tables,
+                             self.heads, self.key_dim, self.rot_dim, self.value_dim, self.kv_rank, group.page_size, self.window,
+                             self.scale)
+        self.o(o, out=residual, accumulate=True)

@@ -56,6 +56,8 @@ class Linear:
 
     def desc(self) -> runtime.LinearDesc:
         runtime.need("gemm_tc" if self.tensor_core else "gemm_plain")
+        if self.tensor_core:
+            runtime.need("gemm_tc_pair")      # the plan of a product of many rows may choose it; a product called on its own has no dry run that would ask for it
         return runtime.LinearDesc(self.weight.data_ptr(), runtime.code(self.weight.dtype), self.out_features,
                                   self.in_features, self.precision.flags)
 

@@ -63,3 +63,37 @@ class GatedMLP(Part):
         s, _keep = call_struct(step, self, h.device, lambda p: rt.llmx_part_workspace(self.native, ctypes.byref(p), rows, -1))
         runtime.check(rt.llmx_ffn_forward(self.native, ctypes.byref(s), h.data_ptr(), rows, residual.data_ptr(), runtime.ptr(cleared)),
                       "feed-forward")
+
+
+class ClampedGLU(Part):
+    """residual += (g sigmoid(alpha g) (u + 1)) Wd^T with g = min(h Wg^T, limit), u = clamp(h Wu^T, -limit, limit).
+
+    The gate is cut from above only, the linear branch on both sides and shifted by one; `limit` and `alpha` are
+    arguments.  Gate and up weights are stacked so one product gives both; the activation is `llmx_clamped_glu`
+    (csrc/rowwise.cu) in 32-bit.  `names`: the three tensors' roles."""
+
+    def __init__(self, hidden: int, intermediate: int, limit: float, alpha: float = 1.702, names=("gate", "up", "down")):
+        self.hidden, self.intermediate = int(hidden), int(intermediate)
+        self.limit, self.alpha, self.names = float(limit), float(alpha), tuple(names)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        g, u, d = self.names
+        return {g: TensorSpec((self.intermediate, self.hidden)), u: TensorSpec((self.intermediate, self.hidden)),
+                d: TensorSpec((self.hidden, self.intermediate))}
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        g, u, d = self.names
+        self.gate_up = Linear(torch.cat([tensors[g], tensors[u]], dim=0), precision)
+        self.down = Linear(tensors[d], precision)
+
+    def forward(self, h: torch.Tensor, step: Optional[StepBatch], residual: torch.Tensor) -> None:
+        from .. import ops
+        rows = h.shape[0]
+        if not (h.is_cuda and h.is_contiguous() and h.dtype is self.precision.act and tuple(h.shape) == (rows, self.hidden)
+                and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
+            raise runtime.KernelError("feed-forward: rows of the path's type and the part's width, a float32 residual")
+        gu = self.gate_up(h)
+        act = torch.empty((rows, self.intermediate), dtype=self.precision.act, device=h.device)
+        ops.clamped_glu(gu, act, self.limit, self.alpha)
+        self.down(act, out=residual, accumulate=True)

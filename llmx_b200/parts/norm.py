@@ -56,3 +56,32 @@ class RMSNorm(Part):
                                                       runtime.ptr(row_index), rows, runtime.ptr(zero),
                                                       0 if zero is None else zero.numel()), "rmsnorm")
         return out
+
+
+class LayerNorm(Part):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w, var the mean of squared deviations; a weight and no bias; 32-bit
+    arithmetic (csrc/rowwise.cu, `llmx_layernorm`).  `role`: the weight's tensor role ("" names it by the part's
+    prefix alone).  The same interface as RMSNorm; it has no twin in the native runtime, so a block that holds it is
+    walked from Python."""
+
+    def __init__(self, width: int, eps: float, role: str = "weight"):
+        self.width, self.eps, self.role = int(width), float(eps), role
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.role: TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        self.weight = tensors[self.role].to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .. import ops
+        if zero is not None:
+            zero.zero_()
+        rows = x.shape[0] if row_index is None else row_index.numel()
+        if out is None:
+            out = torch.empty((rows, self.width), dtype=out_dtype or self.precision.act, device=x.device)
+        return ops.layernorm(x, self.weight, self.eps, out, row_index)

@@ -53,10 +53,15 @@ def registered_names() -> Tuple[str, ...]:
 
 
 def architecture_of(raw_config: Dict[str, Any]) -> ArchitectureEntry:
-    """The entry config.json names, by `architectures[0]` first, then `model_type`."""
+    """The entry config.json names, by `architectures[0]` first, then `model_type`, then a plain `architecture` string."""
     _ensure_builtin()
     archs = raw_config.get("architectures")
     tried = []
+    single = raw_config.get("architecture")
+    if isinstance(single, str) and archs is None and "model_type" not in raw_config:
+        tried.append(single)
+        if single in _BY_NAME:
+            return _BY_NAME[single]
     if isinstance(archs, list) and len(archs) == 1 and isinstance(archs[0], str):
         tried.append(archs[0])
         if archs[0] in _BY_NAME:
@@ -86,3 +91,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_done = True
     from .models import qwen3 as _qwen3  # noqa: F401  (registers itself)
+    from .models import buzetar as _buzetar  # noqa: F401

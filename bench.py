@@ -124,6 +124,101 @@ def reference_arm(args):
     return arm.main(args, raw, args.size)
 
 
+# Layer sizes for `--design buzetar`: a Buzetar of `layers` layers (its three mixers in turn) beside a dense Qwen3 of the
+# same width, depth, feed-forward width and head count.
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=6144, vocab=32768, q_rank=768, kv_rank=512, rot=64, window=2048, layers=6),
+    "w4096": dict(width=4096, heads=32, ff=12288, vocab=32768, q_rank=1536, kv_rank=512, rot=64, window=4096, layers=3),
+}
+
+
+def design_bench(args) -> int:
+    """`--design buzetar`: a 2,048-token prompt and decode steps of --batch requests after --context tokens, for Buzetar
+    and for a Qwen3 of equal size, bfloat16, random weights, with the device time by kernel of one plain step of each."""
+    import statistics
+    import torch
+    from llmx_b200 import ops
+    from llmx_b200.config import BuzetarConfig, Qwen3Config
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.engine.decode_loop import DecodeSession
+    torch.cuda.set_device(0)
+    host_gen = torch.Generator()
+    host_gen.manual_seed(2)
+    page, T, B, C = 16, args.prefill_tokens, args.batch, args.context
+    out = {"design": "buzetar", "dtype": "bf16", "data": "synthetic", "prefill_tokens": T, "batch": B, "context": C,
+           "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+    for name in (args.design_size.split(",") if args.design_size else sorted(DESIGN_SIZES)):
+        z = DESIGN_SIZES[name]
+        E, H, F, L = z["width"], z["heads"], z["ff"], z["layers"]
+        mlp = {"kind": "dense", "ff": F, "limit": 7.0}
+        kinds = [
+            {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * h / H) for h in range(H)]}, "mlp": mlp},
+            {"type": "latent_attention", "mixer": {"heads": H, "dim": 128, "rot_dim": z["rot"], "vdim": 128, "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+                                                   "scale": (128 + z["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot"]}, "mask": {"size": z["window"]}}, "mlp": mlp},
+            {"type": "delta", "mixer": {"heads": H, "kv_heads": H // 2, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}]
+        buz = BuzetarConfig.from_dict({"architecture": "Buzetar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                                       "logit_scale": 1.0, "layers": [kinds[i % 3] for i in range(L)]})
+        qwen = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=L, hidden_size=E, intermediate_size=F, num_attention_heads=H,
+                                          num_key_value_heads=max(H // 4, 1), vocab_size=z["vocab"]))
+        res = {}
+        for tag, cfg in (("buzetar", buz), ("qwen3", qwen)):
+            per_request = -(-(C + 3 * args.steps + args.warmup + 64) // page) * page
+            engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=max(B * per_request, T + page),
+                                                                           page_size=page, max_requests=B, record_after=2))
+            vocab = z["vocab"]
+            prompt = torch.randint(0, vocab, (T,), generator=host_gen).tolist()
+            times = []
+            for i in range(3 + 5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry("prefill", prompt, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.end("prefill")
+                if i >= 3:
+                    times.append(e0.elapsed_time(e1))
+            with ops.kernel_times() as kt:
+                engine.step([StepEntry("prefill", prompt, [T - 1])])
+            engine.end("prefill")
+            pf_ms = statistics.median(times)
+            r = {"prefill_tok_s": round(T * 1e3 / pf_ms, 1), "prefill_ms": round(pf_ms, 3),
+                 "prefill_ms_by_kernel": {k: round(v[1], 4) for k, v in sorted(kt.by_function.items(), key=lambda kv: -kv[1][1])}}
+            rids = [("bench", i) for i in range(B)]
+            for rid in rids:                                     # room for the history without running it (zeros: a step's cost
+                rc = engine.cache.new_request(rid)               # depends on how much it reads, not on what)
+                rc.prepare(C)
+                rc.commit()
+            with ops.kernel_times() as kt:
+                engine.step([StepEntry(rid, [1], [0]) for rid in rids])
+            r["decode_ms_by_kernel"] = {k: round(v[1], 4) for k, v in sorted(kt.by_function.items(), key=lambda kv: -kv[1][1])}
+            session = DecodeSession(engine, rids)
+            tokens = torch.randint(0, vocab, (B,), generator=host_gen).tolist()
+            for _ in range(max(args.warmup, 3)):
+                session.step(tokens)
+            torch.cuda.synchronize()
+            launches0 = ops.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                session.step(tokens)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            r.update(decode_tok_s=round(B * 1e3 / ms, 1), decode_ms_per_step=round(ms, 4), gpu_launches=ops.launch_count() - launches0)
+            session.close()
+            for rid in rids:
+                engine.end(rid)
+            res[tag] = r
+            del engine, session
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+        res["config"] = dict(z)
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -140,9 +235,18 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill", "sample"], default=None,
                     help="run one part only (for profiling); the line then holds only that part")
+    ap.add_argument("--design", choices=["buzetar"], default=None,
+                    help="instead of the default workload: prompt and decode throughput of this design at sizes that resemble a "
+                         "real model's layers, beside a Qwen3 of equal size (one JSON line of its own)")
+    ap.add_argument("--design-size", default=None, help="with --design: one of " + ", ".join(sorted(DESIGN_SIZES)) + " (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        if args.gpus != 1:
+            print(f"bench.py measures one GPU; --gpus {args.gpus} is not built in this engine")
+            return 2
+        return design_bench(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built in this engine")
         return 2

@@ -186,7 +186,456 @@ int launch_attention(int pl, dim3 grid, size_t smem, cudaStream_t stream, const 
 #undef LLMX_LAT
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// The tiled form: three kernels.
+//   latent_query   one block per (row, head): rotation, the key map, the scale -> qk [rows, heads, C + R] floats
+//   latent_scores  one block per (tile of rows, group of heads, range of keys): 16 (row, head) pairs, two to a warp,
+//                  share every key: a tile of keys is copied from the pages into shared memory once (the next tile's
+//                  copy in flight in registers meanwhile) and each warp walks it for its two pairs, a lane holding
+//                  neighbouring pairs of a key's values; partial (sum of weighted latents, maximum, sum) per range
+//   latent_merge   one block per (row, head): the ranges merged in order, then the value map
+// Prompt portions fill the grid with row tiles; decoding rows, few and with long histories, with key ranges.
+// ---------------------------------------------------------------------------------------------------------------
+// ROWS_Q: rows a block of the query or the merge kernel holds: a map's weights are read once for them (8 when a step has
+// many rows; 1 when it has few, so that the blocks are many).
+template <typename WT, int ROWS_Q>
+__global__ void __launch_bounds__(128)
+latent_query_kernel(const float* __restrict__ q, int q_stride, const WT* __restrict__ w_uk, float* __restrict__ qk,
+                    const float* __restrict__ freq, int rot_pairs, const int* __restrict__ positions, int rows, int heads,
+                    int D, int R, int C, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float qraw[];            // ROWS_Q * (D + R)
+    const int r0 = blockIdx.x * ROWS_Q, h = blockIdx.y;
+    const int n = min(ROWS_Q, rows - r0);
+    const int DR = D + R;
+    for (int i = threadIdx.x; i < ROWS_Q * DR; i += blockDim.x) {
+        const int r = i / DR;
+        qraw[i] = r < n ? q[(size_t)(r0 + r) * q_stride + (size_t)h * DR + i % DR] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * (R / 2); i += blockDim.x) {
+        const int r = i / (R / 2), k = i % (R / 2);
+        const float a = qraw[r * DR + D + 2 * k], b = qraw[r * DR + D + 2 * k + 1];
+        float ra = a, rb = b;
+        if (k < rot_pairs) {
+            float sn, cs;
+            sincosf((float)positions[r0 + r] * freq[k], &sn, &cs);
+            ra = a * cs - b * sn;
+            rb = b * cs + a * sn;
+        }
+        float* dst = qk + ((size_t)(r0 + r) * heads + h) * (C + R) + C;
+        dst[2 * k] = ra * scale;
+        dst[2 * k + 1] = rb * scale;
+    }
+    if ((R & 1) && (int)threadIdx.x < n)
+        qk[((size_t)(r0 + threadIdx.x) * heads + h) * (C + R) + C + R - 1] = qraw[threadIdx.x * DR + DR - 1] * scale;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const WT* col = w_uk + (size_t)h * D * C + c;
+        float s[ROWS_Q];
+#pragma unroll
+        for (int r = 0; r < ROWS_Q; ++r) s[r] = 0.0f;
+        for (int d = 0; d < D; ++d) {
+            const float w = to_float(col[(size_t)d * C]);
+#pragma unroll
+            for (int r = 0; r < ROWS_Q; ++r) s[r] = fmaf(qraw[r * DR + d], w, s[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS_Q; ++r)
+            if (r < n) qk[((size_t)(r0 + r) * heads + h) * (C + R) + c] = s[r] * scale;
+    }
+}
+
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+constexpr int TILE_THREADS = 256;
+
+// PLP: neighbouring pairs of a key's values a lane holds (C + R <= 64 * PLP; FULL: equal, so no value is out of range).
+// A tile has 64 / sizeof(KVT) keys.
+template <typename KVT, int PLP, bool FULL>
+__global__ void __launch_bounds__(TILE_THREADS)
+latent_scores_kernel(const float* __restrict__ qk, const KVT* __restrict__ cache, float* __restrict__ part,
+                     const int* __restrict__ tiles, const int* __restrict__ row_request, const int* __restrict__ positions,
+                     const int* __restrict__ block_tables, int table_stride, int heads, int C, int R, int HT, int splits,
+                     int page_size, int window) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int KT = 64 / (int)sizeof(KVT);
+    extern __shared__ __align__(16) unsigned char tile_mem[];
+    const int W = C + R, Wp = (W + 1) & ~1;
+    KVT* bufs[2] = {reinterpret_cast<KVT*>(tile_mem), reinterpret_cast<KVT*>(tile_mem) + (size_t)KT * Wp};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = tiles[2 * blockIdx.x], tile_rows = tiles[2 * blockIdx.x + 1];
+    const int half = HT / 2;
+    const int my_row = warp / half;
+    const int h0 = blockIdx.y * HT + 2 * (warp % half), h1 = h0 + 1;
+    const bool row_ok = my_row < tile_rows;
+    const int row = row0 + (row_ok ? my_row : 0);
+    const int pos = positions[row];
+    const int lo_row = window > 0 ? max(0, pos - window + 1) : 0;
+    // The block's keys: from the first row's lowest to the last row's own, cut into `splits` ranges of whole tiles.
+    const int pos_first = positions[row0], pos_last = positions[row0 + tile_rows - 1];
+    const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int total = pos_last + 1 - lo;
+    const int chunk = ((total + splits - 1) / splits + KT - 1) / KT * KT;
+    const int begin = lo + (int)blockIdx.z * chunk;
+    const int end = min(begin + chunk, pos_last + 1);
+    const int* table = block_tables + (size_t)row_request[row0] * table_stride;
+
+    float q0[2 * PLP], q1[2 * PLP], acc0[2 * PLP], acc1[2 * PLP];
+#pragma unroll
+    for (int i = 0; i < PLP; ++i)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int e = 2 * lane + 64 * i + u;
+            q0[2 * i + u] = (row_ok && h0 < heads && e < W) ? qk[((size_t)row * heads + h0) * W + e] : 0.0f;
+            q1[2 * i + u] = (row_ok && h1 < heads && e < W) ? qk[((size_t)row * heads + h1) * W + e] : 0.0f;
+            acc0[2 * i + u] = 0.0f;
+            acc1[2 * i + u] = 0.0f;
+        }
+    float m0 = -INFINITY, l0 = 0.0f, m1 = -INFINITY, l1 = 0.0f;
+
+    const int row_bytes = W * (int)sizeof(KVT);
+    const bool vec = (row_bytes % 16) == 0;
+    const int per_row = row_bytes / 16;                 // 16-byte pieces a key has (vector path)
+    const int pieces = KT * per_row;
+    uint4 stage[PLP];
+    auto fetch = [&](int t0) {
+#pragma unroll
+        for (int j = 0; j < PLP; ++j) {
+            const int c = threadIdx.x + j * TILE_THREADS;
+            stage[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (c < pieces) {
+                const int key = c / per_row, t = t0 + key;
+                if (t < end) {
+                    const KVT* src = cache + ((size_t)table[t / page_size] * page_size + t % page_size) * W;
+                    stage[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(src) + (size_t)(c % per_row) * 16);
+                }
+            }
+        }
+    };
+    auto stash = [&](KVT* buf) {
+#pragma unroll
+        for (int j = 0; j < PLP; ++j) {
+            const int c = threadIdx.x + j * TILE_THREADS;
+            if (c < pieces)
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(buf) + ((size_t)(c / per_row) * Wp * sizeof(KVT)) + (size_t)(c % per_row) * 16) = stage[j];
+        }
+    };
+    auto copy_plain = [&](KVT* buf, int t0) {          // rows that are no multiple of 16 bytes: value by value
+        for (int i = threadIdx.x; i < KT * Wp; i += TILE_THREADS) {
+            const int key = i / Wp, e = i % Wp, t = t0 + key;
+            KVT v = from_float<KVT>(0.0f);
+            if (t < end && e < W) v = cache[((size_t)table[t / page_size] * page_size + t % page_size) * W + e];
+            buf[i] = v;
+        }
+    };
+
+    const int n_tiles = end > begin ? (end - begin + KT - 1) / KT : 0;
+    if (n_tiles > 0) {
+        if (vec) {
+            fetch(begin);
+            stash(bufs[0]);
+        } else {
+            copy_plain(bufs[0], begin);
+        }
+    }
+    __syncthreads();
+    for (int it = 0; it < n_tiles; ++it) {
+        const int t0 = begin + it * KT;
+        const bool more = it + 1 < n_tiles;
+        if (more && vec) fetch(t0 + KT);
+        const KVT* buf = bufs[it & 1];
+        if (row_ok) {
+            const int j_hi = min(KT, min(end, pos + 1) - t0);
+            int j = max(0, lo_row - t0);
+            // Two keys a turn: their sums over the lanes and their exponentials overlap; the last odd key goes alone.
+            for (; j + 1 < j_hi; j += 2) {
+                const KVT* ka_row = buf + (size_t)j * Wp;
+                const KVT* kb_row = ka_row + Wp;
+                float ka[2 * PLP], kb[2 * PLP];
+                float s0a = 0.0f, s1a = 0.0f, s0b = 0.0f, s1b = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PLP; ++i) {
+                    const int e = 2 * lane + 64 * i;
+                    const float2 x = (FULL || e < Wp) ? load2(ka_row + e) : make_float2(0.0f, 0.0f);
+                    const float2 y = (FULL || e < Wp) ? load2(kb_row + e) : make_float2(0.0f, 0.0f);
+                    ka[2 * i] = x.x;
+                    ka[2 * i + 1] = x.y;
+                    kb[2 * i] = y.x;
+                    kb[2 * i + 1] = y.y;
+                    s0a = fmaf(q0[2 * i], x.x, s0a);
+                    s1a = fmaf(q1[2 * i], x.x, s1a);
+                    s0b = fmaf(q0[2 * i], y.x, s0b);
+                    s1b = fmaf(q1[2 * i], y.x, s1b);
+                    s0a = fmaf(q0[2 * i + 1], x.y, s0a);
+                    s1a = fmaf(q1[2 * i + 1], x.y, s1a);
+                    s0b = fmaf(q0[2 * i + 1], y.y, s0b);
+                    s1b = fmaf(q1[2 * i + 1], y.y, s1b);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    s0a += __shfl_xor_sync(0xffffffffu, s0a, o);
+                    s1a += __shfl_xor_sync(0xffffffffu, s1a, o);
+                    s0b += __shfl_xor_sync(0xffffffffu, s0b, o);
+                    s1b += __shfl_xor_sync(0xffffffffu, s1b, o);
+                }
+                const float n0 = fmaxf(s0a, s0b), n1 = fmaxf(s1a, s1b);
+                if (n0 > m0) {
+                    const float corr = expf(m0 - n0);
+                    l0 *= corr;
+#pragma unroll
+                    for (int i = 0; i < 2 * PLP; ++i) acc0[i] *= corr;
+                    m0 = n0;
+                }
+                if (n1 > m1) {
+                    const float corr = expf(m1 - n1);
+                    l1 *= corr;
+#pragma unroll
+                    for (int i = 0; i < 2 * PLP; ++i) acc1[i] *= corr;
+                    m1 = n1;
+                }
+                const float p0a = expf(s0a - m0), p0b = expf(s0b - m0), p1a = expf(s1a - m1), p1b = expf(s1b - m1);
+                l0 += p0a + p0b;
+                l1 += p1a + p1b;
+#pragma unroll
+                for (int i = 0; i < 2 * PLP; ++i) {
+                    acc0[i] = fmaf(p0b, kb[i], fmaf(p0a, ka[i], acc0[i]));
+                    acc1[i] = fmaf(p1b, kb[i], fmaf(p1a, ka[i], acc1[i]));
+                }
+            }
+            for (; j < j_hi; ++j) {
+                const KVT* krow = buf + (size_t)j * Wp;
+                float kv[2 * PLP];
+                float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PLP; ++i) {
+                    const int e = 2 * lane + 64 * i;
+                    const float2 x = (FULL || e < Wp) ? load2(krow + e) : make_float2(0.0f, 0.0f);
+                    kv[2 * i] = x.x;
+                    kv[2 * i + 1] = x.y;
+                    s0 = fmaf(q0[2 * i], x.x, s0);
+                    s0 = fmaf(q0[2 * i + 1], x.y, s0);
+                    s1 = fmaf(q1[2 * i], x.x, s1);
+                    s1 = fmaf(q1[2 * i + 1], x.y, s1);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                }
+                if (s0 > m0) {
+                    const float corr = expf(m0 - s0);
+                    l0 *= corr;
+#pragma unroll
+                    for (int i = 0; i < 2 * PLP; ++i) acc0[i] *= corr;
+                    m0 = s0;
+                }
+                if (s1 > m1) {
+                    const float corr = expf(m1 - s1);
+                    l1 *= corr;
+#pragma unroll
+                    for (int i = 0; i < 2 * PLP; ++i) acc1[i] *= corr;
+                    m1 = s1;
+                }
+                const float p0 = expf(s0 - m0), p1 = expf(s1 - m1);
+                l0 += p0;
+                l1 += p1;
+#pragma unroll
+                for (int i = 0; i < 2 * PLP; ++i) {
+                    acc0[i] = fmaf(p0, kv[i], acc0[i]);
+                    acc1[i] = fmaf(p1, kv[i], acc1[i]);
+                }
+            }
+        }
+        if (more) {
+            if (vec) stash(bufs[(it + 1) & 1]);
+            else copy_plain(bufs[(it + 1) & 1], t0 + KT);
+        }
+        __syncthreads();
+    }
+    if (!row_ok) return;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int h = u == 0 ? h0 : h1;
+        if (h >= heads) continue;
+        float* dst = part + (((size_t)row * heads + h) * splits + blockIdx.z) * (C + 2);
+#pragma unroll
+        for (int i = 0; i < 2 * PLP; ++i) {
+            const int e = 2 * lane + 64 * (i >> 1) + (i & 1);
+            if (e < C) dst[e] = u == 0 ? acc0[i] : acc1[i];
+        }
+        if (lane == 0) {
+            dst[C] = u == 0 ? m0 : m1;
+            dst[C + 1] = u == 0 ? l0 : l1;
+        }
+    }
+}
+
+template <typename WT, int ROWS_Q>
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part, const WT* __restrict__ w_uv, WT* __restrict__ out, int rows, int heads,
+                    int V, int C, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float lat[];             // ROWS_Q * C
+    const int r0 = blockIdx.x * ROWS_Q, h = blockIdx.y;
+    const int n = min(ROWS_Q, rows - r0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = 0; r < ROWS_Q; ++r) {
+        if (r >= n) {
+            for (int c = threadIdx.x; c < C; c += blockDim.x) lat[r * C + c] = 0.0f;
+            continue;
+        }
+        const float* src = part + ((size_t)(r0 + r) * heads + h) * splits * (C + 2);
+        float mm = -INFINITY;
+        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[(size_t)s * (C + 2) + C]);
+        float ll = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = src[(size_t)s * (C + 2) + C];
+            ll += ms == -INFINITY ? 0.0f : src[(size_t)s * (C + 2) + C + 1] * expf(ms - mm);
+        }
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float o = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+                const float ms = src[(size_t)s * (C + 2) + C];
+                if (ms != -INFINITY) o = fmaf(src[(size_t)s * (C + 2) + c], expf(ms - mm), o);
+            }
+            lat[r * C + c] = o / ll;
+        }
+    }
+    __syncthreads();
+    for (int v = warp; v < V; v += 4) {
+        const WT* wr = w_uv + ((size_t)h * V + v) * C;
+        float s[ROWS_Q];
+#pragma unroll
+        for (int r = 0; r < ROWS_Q; ++r) s[r] = 0.0f;
+        for (int c = lane; c < C; c += 32) {
+            const float w = to_float(wr[c]);
+#pragma unroll
+            for (int r = 0; r < ROWS_Q; ++r) s[r] = fmaf(w, lat[r * C + c], s[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS_Q; ++r) {
+            const float t = warp_sum(s[r]);
+            if (lane == 0 && r < n) out[((size_t)(r0 + r) * heads + h) * V + v] = from_float<WT>(t);
+        }
+    }
+}
+
+template <typename KVT>
+int launch_scores(int plp, dim3 grid, size_t smem, cudaStream_t stream, const float* qk, const void* cache, float* part,
+                  const int* tiles, const int* row_request, const int* positions, const int* block_tables, int table_stride,
+                  int heads, int C, int R, int HT, int splits, int page_size, int window) {
+#define LLMX_SC(P)                                                                                                        \
+    do {                                                                                                                  \
+        if (C + R == 64 * P) {                                                                                            \
+            if (smem > 48 * 1024)                                                                                         \
+                cudaFuncSetAttribute(latent_scores_kernel<KVT, P, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            launch_kernel(latent_scores_kernel<KVT, P, true>, grid, dim3(TILE_THREADS), smem, stream, qk, (const KVT*)cache, \
+                          part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits,     \
+                          page_size, window);                                                                             \
+        } else {                                                                                                          \
+            if (smem > 48 * 1024)                                                                                         \
+                cudaFuncSetAttribute(latent_scores_kernel<KVT, P, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            launch_kernel(latent_scores_kernel<KVT, P, false>, grid, dim3(TILE_THREADS), smem, stream, qk, (const KVT*)cache, \
+                          part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits,     \
+                          page_size, window);                                                                             \
+        }                                                                                                                 \
+    } while (0)
+    if (plp <= 1) LLMX_SC(1);
+    else if (plp <= 2) LLMX_SC(2);
+    else if (plp <= 4) LLMX_SC(4);
+    else if (plp <= 6) LLMX_SC(6);
+    else if (plp <= 9) LLMX_SC(9);
+    else if (plp <= 12) LLMX_SC(12);
+    else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_SC
+    return launch_status();
+}
 }  // namespace
+
+// How the tiled form cuts a step: heads a block holds (even, at most 16), rows a tile holds (16 / that).
+LLMX_EXPORT void llmx_latent_tile_shape(int heads, int* heads_per_block, int* rows_per_tile) {
+    int ht = (heads + 1) & ~1;
+    ht = ht > 16 ? 16 : ht;
+    while (16 % ht) ht += 2;                   // 2, 4, 8 or 16
+    *heads_per_block = ht;
+    *rows_per_tile = 16 / ht;
+}
+
+// The tiled form's three steps, each an entry point of its own (so that each shows in a profile).  Shapes as in
+// llmx_latent_attention.  qk: float [rows, heads, C + R]; part: float [rows, heads, splits, C + 2].
+LLMX_EXPORT int llmx_latent_query(const float* q, int q_stride, const void* w_uk, int w_dtype, float* qk, const float* freq,
+                                  int rot_pairs, const int* positions, int rows, int heads, int D, int R, int C, float scale,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || D <= 0 || R < 0 || C <= 0 || 2 * rot_pairs > R) return LLMX_ERR_BAD_ARGUMENT;
+    const int rq = rows > 64 ? 8 : 1;
+    const size_t smem = (size_t)rq * (D + R) * sizeof(float);
+    if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
+    const dim3 grid((rows + rq - 1) / rq, heads);
+#define LLMX_Q(WT, RQ)                                                                                                    \
+    launch_kernel(latent_query_kernel<WT, RQ>, grid, dim3(128), smem, stream, q, q_stride, (const WT*)w_uk, qk, freq,      \
+                  rot_pairs, positions, rows, heads, D, R, C, scale)
+    if (w_dtype == LLMX_BF16) {
+        if (rq == 8) LLMX_Q(__nv_bfloat16, 8);
+        else LLMX_Q(__nv_bfloat16, 1);
+    } else if (w_dtype == LLMX_F32) {
+        if (rq == 8) LLMX_Q(float, 8);
+        else LLMX_Q(float, 1);
+    } else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_Q
+    return launch_status();
+}
+
+// `tiles` (device, int32 [n_tiles, 2]): first row and number of rows (at most the tile shape's) of every row tile, rows
+// of one request each; `splits`: ranges the keys of a tile are cut into.
+LLMX_EXPORT int llmx_latent_scores(const float* qk, const void* cache, int cache_dtype, float* part, const int* tiles,
+                                   int n_tiles, int splits, const int* row_request, const int* positions,
+                                   const int* block_tables, int table_stride, int heads, int C, int R, int page_size,
+                                   int window, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (heads <= 0 || R < 0 || C <= 0 || page_size <= 0 || splits <= 0 || splits > 65535) return LLMX_ERR_BAD_ARGUMENT;
+    const int W = C + R, Wp = (W + 1) & ~1;
+    const int plp = (W + 63) / 64;
+    int HT, RT;
+    llmx_latent_tile_shape(heads, &HT, &RT);
+    const dim3 grid(n_tiles, (heads + HT - 1) / HT, splits);
+    const size_t smem = (size_t)2 * 64 * Wp;          // two tiles of 64 / sizeof(element) keys
+    if (smem > 200 * 1024) return LLMX_ERR_UNSUPPORTED;
+    if (cache_dtype == LLMX_BF16)
+        return launch_scores<__nv_bfloat16>(plp, grid, smem, stream, qk, cache, part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits, page_size, window);
+    if (cache_dtype == LLMX_F32)
+        return launch_scores<float>(plp, grid, smem, stream, qk, cache, part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits, page_size, window);
+    return LLMX_ERR_UNSUPPORTED;
+}
+
+LLMX_EXPORT int llmx_latent_merge(const float* part, const void* w_uv, int w_dtype, void* out, int rows, int heads, int V,
+                                  int C, int splits, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || V <= 0 || C <= 0 || splits <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    const int rq = rows > 64 ? 8 : 1;
+    const size_t smem = (size_t)rq * C * sizeof(float);
+    if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
+    const dim3 grid((rows + rq - 1) / rq, heads);
+#define LLMX_M(WT, RQ)                                                                                                    \
+    launch_kernel(latent_merge_kernel<WT, RQ>, grid, dim3(128), smem, stream, part, (const WT*)w_uv, (WT*)out, rows,      \
+                  heads, V, C, splits)
+    if (w_dtype == LLMX_BF16) {
+        if (rq == 8) LLMX_M(__nv_bfloat16, 8);
+        else LLMX_M(__nv_bfloat16, 1);
+    } else if (w_dtype == LLMX_F32) {
+        if (rq == 8) LLMX_M(float, 8);
+        else LLMX_M(float, 1);
+    } else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_M
+    return launch_status();
+}
 
 // dkv float [rows, stride]: C latent values then R rotated-part values; w float [C]; freq float [rot_pairs];
 // slots[row] = page * page_size + offset (negative: skip the row); cache [pages * page_size, C + R] of `cache_dtype`.

@@ -7,12 +7,12 @@
 //     S  <- a_t * S + k_t u_t^T
 //     o_t = S^T q_t                                        (the read-out sees the row's own write)
 // Column j of S (the D values that meet v's entry j) never meets another column, so the work is cut by columns:
-// LANES threads own one column, each holding D / LANES of its values in registers for all of the request's rows;
-// the two dot products are sums over a lane's values and then over the LANES lanes by shuffles, in an order that the
-// sizes alone fix.  A block holds columns of one head (and of one request); the rows' q and k are read by every
-// worker from the cache.  The state is read from `slot_in` (zeros at a request's first token, whatever the slot
-// holds) and written to `slot_out` once, after the request's last row of the step: a step of one row and a step of
-// a thousand run the same code.  State layout in a slot: [H][V][D] floats, so a worker's column is contiguous.
+// a few threads own one column, each holding a share of its values in registers for all of the request's rows;
+// the two dot products are sums over a lane's values and then over the column's lanes by shuffles.  A block holds
+// columns of one head (and of one request); the rows' q and k are read by every worker from the cache.  The state is
+// read from `slot_in` (zeros at a request's first token, whatever the slot holds) and written to `slot_out` once,
+// after the request's last row of the step.  State layout in a slot: [H][V][D] floats, so a worker's column is
+// contiguous.
 //
 // The short convolution in front of the delta rule lives here too (`llmx_conv_prepare`): a causal filter of
 // `taps` taps per channel over the request's rows, continued from the last taps-1 inputs kept in the state slot,
@@ -22,11 +22,14 @@
 #include <math.h>
 
 namespace {
-constexpr int LANES = 8;            // threads that share one column of the state
-constexpr int COLS = 16;            // columns a block owns (128 threads)
+constexpr int REC_THREADS = 128;
 
-template <int PER, bool DELTA>
-__global__ void __launch_bounds__(LANES * COLS)
+// LANES threads share one column of the state, each holding PER of its D values (D <= LANES * PER); a block of 128
+// threads owns 128 / LANES columns of one head.  Few lanes a column (8) make short sums over the lanes and suit steps of
+// a row or a few; a whole warp a column (32) makes four times as many threads and short chains of multiply-adds, which
+// is what a long run of rows, one after the other, waits on.  A row's q, k, v and gates are fetched one row ahead.
+template <int PER, int LANES, bool DELTA>
+__global__ void __launch_bounds__(REC_THREADS)
 recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int q_stride,
                   int k_stride, int v_stride, const float* __restrict__ decay, const float* __restrict__ gate,
                   const float* __restrict__ beta, int gate_stride, float* __restrict__ state, long long slot_floats,
@@ -35,6 +38,7 @@ recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   int qk_heads, int D, int V) {
     pdl_trigger();
     pdl_wait();
+    constexpr int COLS = REC_THREADS / LANES;
     const int r = blockIdx.x;
     const int blocks_per_head = (V + COLS - 1) / COLS;
     const int h = blockIdx.y / blocks_per_head;
@@ -55,27 +59,34 @@ recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         S[i] = (!fresh && d < D) ? sin_[d] : 0.0f;
     }
     const float dec = DELTA ? 0.0f : decay[h];
-    for (int t = 0; t < n; ++t) {
+    float kk[PER], qq[PER], nk[PER], nq[PER];
+    float u = 0.0f, a = dec, bt = 0.0f, nu = 0.0f, na = dec, nb = 0.0f;
+    auto fetch = [&](int t, float* fk, float* fq, float& fu, float& fa, float& fb) {
         const size_t row = (size_t)(a0 + t);
         const float* qp = q + row * q_stride + (size_t)hq * D;
         const float* kp = k + row * k_stride + (size_t)hq * D;
-        float kk[PER], qq[PER];
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int d = lane + i * LANES;
-            kk[i] = d < D ? kp[d] : 0.0f;
-            qq[i] = d < D ? qp[d] : 0.0f;
+            fk[i] = d < D ? kp[d] : 0.0f;
+            fq[i] = d < D ? qp[d] : 0.0f;
         }
-        float u = v[row * v_stride + (size_t)h * V + j];
-        float a = dec;
+        fu = v[row * v_stride + (size_t)h * V + j];
         if (DELTA) {
-            a = gate[row * gate_stride + h];
+            fa = gate[row * gate_stride + h];
+            fb = beta[row * gate_stride + h];
+        }
+    };
+    fetch(0, kk, qq, u, a, bt);
+    for (int t = 0; t < n; ++t) {
+        if (t + 1 < n) fetch(t + 1, nk, nq, nu, na, nb);
+        if (DELTA) {
             float dot = 0.0f;
 #pragma unroll
             for (int i = 0; i < PER; ++i) dot = fmaf(S[i], kk[i], dot);
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            u = beta[row * gate_stride + h] * (u - a * dot);
+            u = bt * (u - a * dot);
         }
         float acc = 0.0f;
 #pragma unroll
@@ -85,7 +96,15 @@ recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         }
 #pragma unroll
         for (int o = LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (live && lane == 0) out[row * ((size_t)heads * V) + (size_t)h * V + j] = acc;
+        if (live && lane == 0) out[(size_t)(a0 + t) * ((size_t)heads * V) + (size_t)h * V + j] = acc;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            kk[i] = nk[i];
+            qq[i] = nq[i];
+        }
+        u = nu;
+        a = DELTA ? na : dec;
+        bt = nb;
     }
     if (live) {
         float* sout = state + (size_t)slot_out[r] * slot_floats + ((size_t)h * V + j) * D;
@@ -119,7 +138,7 @@ conv_prepare_kernel(const float* __restrict__ proj, int stride, int channels, in
         const float* old = state + (size_t)slot_in[r] * slot_floats + conv_off;
         float* fresh = state + (size_t)slot_out[r] * slot_floats + conv_off;
         for (int c = threadIdx.x; c < channels; c += blockDim.x)
-            for (int s = 0; s < keep; ++s) {         // ascending: in place (slot_in == slot_out) reads run ahead of writes
+            for (int s = 0; s < keep; ++s) {         // slot_in and slot_out differ: the rows' blocks read the old inputs meanwhile
                 const int ii = n - keep + s;         // the input's place relative to the step's first row
                 float x = 0.0f;
                 if (ii >= 0) x = proj[(size_t)(a0 + ii) * stride + c];
@@ -164,22 +183,34 @@ conv_prepare_kernel(const float* __restrict__ proj, int stride, int channels, in
 }
 
 template <bool DELTA>
-int launch_recurrence(int per, dim3 grid, cudaStream_t stream, const float* q, const float* k, const float* v, int q_stride,
-                      int k_stride, int v_stride, const float* decay, const float* gate, const float* beta, int gate_stride,
-                      float* state, long long slot_floats, const int* row_start, const int* row_count, const int* history,
-                      const int* slot_in, const int* slot_out, float* out, int heads, int qk_heads, int D, int V) {
-#define LLMX_REC(P)                                                                                                       \
-    launch_kernel(recurrence_kernel<P, DELTA>, grid, dim3(LANES * COLS), 0, stream, q, k, v, q_stride, k_stride, v_stride,  \
-                  decay, gate, beta, gate_stride, state, slot_floats, row_start, row_count, history, slot_in, slot_out,  \
-                  out, heads, qk_heads, D, V)
-    if (per <= 2) LLMX_REC(2);
-    else if (per <= 4) LLMX_REC(4);
-    else if (per <= 8) LLMX_REC(8);
-    else if (per <= 16) LLMX_REC(16);
-    else if (per <= 32) LLMX_REC(32);
-    else return LLMX_ERR_UNSUPPORTED;
+int launch_recurrence(int D, bool wide, int requests, cudaStream_t stream, const float* q, const float* k, const float* v,
+                      int q_stride, int k_stride, int v_stride, const float* decay, const float* gate, const float* beta,
+                      int gate_stride, float* state, long long slot_floats, const int* row_start, const int* row_count,
+                      const int* history, const int* slot_in, const int* slot_out, float* out, int heads, int qk_heads,
+                      int V) {
+#define LLMX_REC(P, L)                                                                                                    \
+    do {                                                                                                                  \
+        const long long by = (long long)heads * ((V + REC_THREADS / L - 1) / (REC_THREADS / L));                          \
+        if (by > 65535) return LLMX_ERR_UNSUPPORTED;                                                                      \
+        launch_kernel(recurrence_kernel<P, L, DELTA>, dim3(requests, (unsigned)by), dim3(REC_THREADS), 0, stream, q, k, v,  \
+                      q_stride, k_stride, v_stride, decay, gate, beta, gate_stride, state, slot_floats, row_start,       \
+                      row_count, history, slot_in, slot_out, out, heads, qk_heads, D, V);                                \
+        return launch_status();                                                                                           \
+    } while (0)
+    if (wide) {
+        if (D <= 32) LLMX_REC(1, 32);
+        if (D <= 64) LLMX_REC(2, 32);
+        if (D <= 128) LLMX_REC(4, 32);
+        if (D <= 256) LLMX_REC(8, 32);
+    } else {
+        if (D <= 16) LLMX_REC(2, 8);
+        if (D <= 32) LLMX_REC(4, 8);
+        if (D <= 64) LLMX_REC(8, 8);
+        if (D <= 128) LLMX_REC(16, 8);
+        if (D <= 256) LLMX_REC(32, 8);
+    }
 #undef LLMX_REC
-    return launch_status();
+    return LLMX_ERR_UNSUPPORTED;
 }
 }  // namespace
 
@@ -191,22 +222,19 @@ LLMX_EXPORT int llmx_linear_recurrence(const float* q, const float* k, const flo
                                        int v_stride, const float* decay, const float* gate, const float* beta,
                                        int gate_stride, float* state, long long slot_floats, const int* row_start,
                                        const int* row_count, const int* history, const int* slot_in, const int* slot_out,
-                                       float* out, int requests, int heads, int qk_heads, int D, int V,
+                                       float* out, int requests, int heads, int qk_heads, int D, int V, int max_rows,
                                        cudaStream_t stream) {
     if (requests <= 0) return 0;
-    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || D <= 0 || V <= 0 || D > 32 * LANES) return LLMX_ERR_UNSUPPORTED;
+    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || D <= 0 || V <= 0 || D > 256) return LLMX_ERR_UNSUPPORTED;
     if ((decay == nullptr) == (gate == nullptr) || (gate != nullptr && beta == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
-    const long long by = (long long)heads * ((V + COLS - 1) / COLS);
-    if (by > 65535) return LLMX_ERR_UNSUPPORTED;
-    const dim3 grid(requests, (unsigned)by);
-    const int per = (D + LANES - 1) / LANES;
+    const bool wide = max_rows > 8;            // `max_rows`: the most rows one request brings (a matter of speed only)
     if (gate)
-        return launch_recurrence<true>(per, grid, stream, q, k, v, q_stride, k_stride, v_stride, decay, gate, beta, gate_stride,
-                                       state, slot_floats, row_start, row_count, history, slot_in, slot_out, out, heads,
-                                       qk_heads, D, V);
-    return launch_recurrence<false>(per, grid, stream, q, k, v, q_stride, k_stride, v_stride, decay, gate, beta, gate_stride,
-                                    state, slot_floats, row_start, row_count, history, slot_in, slot_out, out, heads, qk_heads,
-                                    D, V);
+        return launch_recurrence<true>(D, wide, requests, stream, q, k, v, q_stride, k_stride, v_stride, decay, gate, beta,
+                                       gate_stride, state, slot_floats, row_start, row_count, history, slot_in, slot_out, out,
+                                       heads, qk_heads, V);
+    return launch_recurrence<false>(D, wide, requests, stream, q, k, v, q_stride, k_stride, v_stride, decay, gate, beta,
+                                    gate_stride, state, slot_floats, row_start, row_count, history, slot_in, slot_out, out, heads,
+                                    qk_heads, V);
 }
 
 // proj [rows, stride]: channels 0 .. channels-1 are q (q_channels), k (k_channels) and v, each of whole heads of

@@ -101,12 +101,15 @@ _SIGNATURES = {
     ("rowwise", "llmx_silu_columns"): [_p, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
     ("recurrence", "llmx_linear_recurrence"): [_p, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, ctypes.c_longlong, _p, _p, _p, _p,
-                                               _p, _p, _i, _i, _i, _i, _i, _p],
+                                               _p, _p, _i, _i, _i, _i, _i, _i, _p],
     ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p,
                                           ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
     ("latent_attention", "llmx_latent_write"): [_p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
+    ("latent_attention", "llmx_latent_query"): [_p, _i, _p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _p],
+    ("latent_attention", "llmx_latent_scores"): [_p, _p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    ("latent_attention", "llmx_latent_merge"): [_p, _p, _i, _p, _i, _i, _i, _i, _i, _p],
     ("gemm_plain", "llmx_gemm_plain"): [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p],
     ("attention_plain", "llmx_attention_plain"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
 }
@@ -404,7 +407,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
     _check(_fn("recurrence", "llmx_linear_recurrence")(
         _ptr(q), _ptr(k), _ptr(v), qs, ks, vs, _ptr(decay), _ptr(gate), _ptr(beta), gs, _ptr(state), state.shape[1],
         _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out),
-        _ptr(out), step.requests, heads, qk_heads, key_dim, value_dim, _stream()), "linear_recurrence")
+        _ptr(out), step.requests, heads, qk_heads, key_dim, value_dim, int(step.max_row_count), _stream()), "linear_recurrence")
     return out
 
 
@@ -471,4 +474,42 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w
         _ptr(q), q.shape[1], _ptr(cache), _code(cache), _ptr(w_uk), _ptr(w_uv), _code(w_uk), _ptr(out), _ptr(freq), freq.numel(),
         _ptr(row_request), _ptr(positions), _ptr(block_tables), block_tables.shape[1], rows, heads, key_dim, rot, value_dim,
         latent, page_size, int(window or 0), float(scale), _stream()), "latent_attention")
+    return out
+
+
+def latent_tile_shape(heads: int):
+    """(heads a block of the tiled form holds, rows a tile holds): 16 (row, head) pairs share every key they read."""
+    ht = min((heads + 1) & ~1, 16)
+    while 16 % ht:
+        ht += 2
+    return ht, 16 // ht
+
+
+def latent_attention_tiled(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,
+                           freq: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
+                           tiles: torch.Tensor, n_tiles: int, splits: int, heads: int, key_dim: int, rot: int, value_dim: int,
+                           latent: int, page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """`latent_attention` in its tiled form (csrc/latent_attention.cu): `tiles` int32 [n_tiles, 2] on the device, the
+    first row and the row count of every tile (rows of one request, at most `latent_tile_shape`'s); `splits` ranges
+    of a tile's keys run as blocks of their own and are merged."""
+    _cuda(q, cache, w_uk, w_uv, out, freq, row_request, positions, block_tables, tiles)
+    rows = q.shape[0]
+    _need(q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot), "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
+    _need(tuple(w_uk.shape) == (heads * key_dim, latent) and tuple(w_uv.shape) == (heads * value_dim, latent)
+          and w_uk.dtype == w_uv.dtype == out.dtype, "latent_attention: key and value maps do not fit")
+    _need(tuple(out.shape) == (rows, heads * value_dim) and cache.shape[-1] == latent + rot, "latent_attention: output or cache rows do not fit")
+    for t in (row_request, positions, block_tables, tiles):
+        _need(t.dtype == torch.int32, "latent_attention: metadata must be int32")
+    _need(tiles.numel() >= 2 * n_tiles and n_tiles > 0 and splits > 0, "latent_attention: tiles do not fit")
+    qk = torch.empty((rows, heads, latent + rot), dtype=torch.float32, device=q.device)
+    part = torch.empty((rows, heads, splits, latent + 2), dtype=torch.float32, device=q.device)
+    _check(_fn("latent_attention", "llmx_latent_query")(_ptr(q), q.shape[1], _ptr(w_uk), _code(w_uk), _ptr(qk), _ptr(freq), freq.numel(),
+                                                        _ptr(positions), rows, heads, key_dim, rot, latent, float(scale), _stream()),
+           "latent_query")
+    _check(_fn("latent_attention", "llmx_latent_scores")(_ptr(qk), _ptr(cache), _code(cache), _ptr(part), _ptr(tiles), int(n_tiles),
+                                                         int(splits), _ptr(row_request), _ptr(positions), _ptr(block_tables),
+                                                         block_tables.shape[1], heads, latent, rot, page_size, int(window or 0),
+                                                         _stream()), "latent_scores")
+    _check(_fn("latent_attention", "llmx_latent_merge")(_ptr(part), _ptr(w_uv), _code(w_uv), _ptr(out), rows, heads, value_dim, latent,
+                                                        int(splits), _stream()), "latent_merge")
     return out

@@ -22,8 +22,20 @@ import torch
 from .. import ops, runtime
 from ..cache.manager import KVSpec
 from ..weights.spec import TensorSpec
-from .base import Part, Precision, StepBatch
+from .base import Part, PartPlan, Precision, StepBatch, StepShape
 from .linear import Linear
+
+
+class _TilePlan(PartPlan):
+    """The row tiles of a step for the tiled kernels: (first row, rows) per tile, rows of one request each.  They follow
+    the step's row counts alone, so a recorded step's plan never changes."""
+
+    def __init__(self, tiles):
+        self.tiles = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        self.ints = int(self.tiles.size)
+
+    def fill(self, histories, out: np.ndarray) -> None:
+        out[:self.ints] = self.tiles
 
 
 class LatentAttention(Part):
@@ -62,6 +74,26 @@ class LatentAttention(Part):
         i = np.arange(self.rot_dims // 2, dtype=np.float64)
         freq = np.power(np.float64(self.rot_base), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
         self.freq = torch.from_numpy(freq).to(self.w_uk.device)
+        self._sms = torch.cuda.get_device_properties(self.w_uk.device).multi_processor_count if self.w_uk.is_cuda else 148
+
+    # -- how the tiled kernels cut a step (the same on the host when the plan is made and when the step runs) -------
+    def _tiling(self, counts, max_context: int):
+        """(tiles [(first row, rows)], ranges a tile's keys are cut into so that the blocks fill the device twice)."""
+        ht, rt = ops.latent_tile_shape(self.heads)
+        tiles, start = [], 0
+        for n in counts:
+            tiles += [(start + i, min(rt, n - i)) for i in range(0, n, rt)]
+            start += n
+        keys = max(int(max_context), 1) if self.window is None else min(max(int(max_context), 1), self.window + rt - 1)
+        blocks = len(tiles) * -(-self.heads // ht)
+        splits = max(1, min(-(-2 * self._sms // blocks), keys // 128))
+        return tiles, splits
+
+    def plan_step(self, shape: StepShape) -> Optional[PartPlan]:
+        if getattr(self, "precision", None) is None or self.precision.invariant:
+            return None
+        context = shape.room if shape.room > 0 else max(h + c for h, c in zip(shape.histories, shape.counts))
+        return _TilePlan(self._tiling(shape.counts, context)[0])
 
     def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
                 write_cache: bool = True) -> None:
@@ -77,7 +109,16 @@ class LatentAttention(Part):
         ops.rmsnorm(self.dq(h), self.dq_norm, self.norm_eps, cq)
         q = self.uq(cq)
         o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
-        ops.latent_attention(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions, group.block_tables,
-                             self.heads, self.key_dim, self.rot_dim, self.value_dim, self.kv_rank, group.page_size, self.window,
-                             self.scale)
+        tiles = None if self.precision.invariant else step.plan_ints(self)
+        if tiles is not None:
+            # The tiled kernels: 16 (row, head) pairs share the keys they read; key ranges fill the device when rows are few.
+            host_tiles, splits = self._tiling(step.host_row_count, step.max_context)
+            ops.latent_attention_tiled(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions,
+                                       group.block_tables, tiles, len(host_tiles), splits, self.heads, self.key_dim, self.rot_dim,
+                                       self.value_dim, self.kv_rank, group.page_size, self.window, self.scale)
+        else:
+            # One block per (row, head): the schedule follows the sizes alone (an invariant path, or a step without a plan).
+            ops.latent_attention(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions, group.block_tables,
+                                 self.heads, self.key_dim, self.rot_dim, self.value_dim, self.kv_rank, group.page_size, self.window,
+                                 self.scale)
         self.o(o, out=residual, accumulate=True)

@@ -187,7 +187,7 @@ def test_whole_models_under_every_cutting_float32(tmp_path, which):
 
 # Twice the error measured when the budget was frozen, as a fraction of the logit scale (the plain implementation is
 # exact; the path rounds the inputs of products and the cached latents to bfloat16).
-BF16_BUDGET = {"P": 4e-2, "Q": 4e-2}
+BF16_BUDGET = {"P": 3.6e-2, "Q": 2.5e-2}     # measured: P 1.8e-2, Q 1.2e-2, the same under every cutting
 
 
 @pytest.mark.parametrize("which", ["P", "Q"])

@@ -16,6 +16,7 @@
 // Rotation: pairs (2i, 2i + 1), i < dims / 2, of the rotated part turn by angle p * f_i, f_i = base^(-2i / dims), given
 // as a float table; the angle is the float product, its cosine and sine the precise functions.
 #include "common.cuh"
+#include "attn_common.cuh"
 #include <math.h>
 
 namespace {
@@ -527,6 +528,236 @@ latent_merge_kernel(const float* __restrict__ part, const WT* __restrict__ w_uv,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The scores step on the tensor cores (bfloat16 cache, C a multiple of 128 up to 512, C + R a multiple of 32).
+// The 16 (row, head) pairs of a block are the 16 rows of an m16n8k16 product.  A 32-bit factor enters such a product
+// as the sum of three bfloat16 values (x = hi + mid + lo, each the rounding of what the ones before left over): the
+// products with the cache's bfloat16 values are exact and are added in 32-bit, so scores and weights keep 32-bit
+// precision although the instruction takes 16-bit operands, at three instructions for one.
+//   scores: warp w makes S[16 pairs, its 8 keys of the tile's 64] = (Qhi + Qmid + Qlo) K^T over C + R
+//   weights: warp w takes pairs 2w, 2w + 1: mask, running maximum and sum, p = exp(s - m) split three ways
+//   values: warp w owns C / 8 columns of the weighted sum of latents: O = corr O + (Phi + Pmid + Plo) Kc
+// Key tiles come by cp.async into two buffers (rows padded so that fragment loads meet no bank twice).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(hi);
+    mid = __float2bfloat16_rn(r1);
+    lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool real) {
+    const int n = real ? 16 : 0;               // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+constexpr int TC_KT = 64;                      // keys a tile
+constexpr int TC_PS = TC_KT + 8;               // row stride of the weights' three parts (elements)
+constexpr int TC_SS = TC_KT + 4;               // row stride of the scores (floats)
+
+static inline size_t tc_smem_bytes(int W) {
+    const size_t ws = (size_t)W + 8;
+    return 2 * TC_KT * ws * 2 + 3 * 16 * ws * 2 + 3 * 16 * TC_PS * 2 + 16 * TC_SS * 4 + 16 * 4 * 6;
+}
+
+template <int NB>                              // n-blocks of 8 columns a warp owns: C = 64 * NB
+__global__ void __launch_bounds__(TILE_THREADS, 1)
+latent_scores_tc_kernel(const float* __restrict__ qk, const __nv_bfloat16* __restrict__ cache, float* __restrict__ part,
+                        const int* __restrict__ tiles, const int* __restrict__ row_request,
+                        const int* __restrict__ positions, const int* __restrict__ block_tables, int table_stride,
+                        int heads, int C, int R, int HT, int splits, int page_size, int window) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(128) unsigned char tc_mem[];
+    const int W = C + R, WS = W + 8;
+    __nv_bfloat16* keys = reinterpret_cast<__nv_bfloat16*>(tc_mem);                 // [2][TC_KT][WS]
+    __nv_bfloat16* qs = keys + (size_t)2 * TC_KT * WS;                              // [3][16][WS]
+    __nv_bfloat16* ps = qs + (size_t)3 * 16 * WS;                                   // [3][16][TC_PS]
+    float* ss = reinterpret_cast<float*>(ps + 3 * 16 * TC_PS);                      // [16][TC_SS]
+    float* row_m = ss + 16 * TC_SS;                                                 // [16] running maximum
+    float* row_l = row_m + 16;                                                      // [16] running sum
+    float* row_c = row_l + 16;                                                      // [16] this tile's correction
+    int* pair_row = reinterpret_cast<int*>(row_c + 16);                             // [16] row of the pair, or -1
+    int* pair_lo = pair_row + 16;
+    int* pair_pos = pair_lo + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c2 = (lane & 3) * 2;
+    const int row0 = tiles[2 * blockIdx.x], tile_rows = tiles[2 * blockIdx.x + 1];
+    const int pos_first = positions[row0], pos_last = positions[row0 + tile_rows - 1];
+    const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int total = pos_last + 1 - lo;
+    const int chunk = ((total + splits - 1) / splits + TC_KT - 1) / TC_KT * TC_KT;
+    const int begin = lo + (int)blockIdx.z * chunk;
+    const int end = min(begin + chunk, pos_last + 1);
+    const int* table = block_tables + (size_t)row_request[row0] * table_stride;
+
+    if (threadIdx.x < 16) {
+        const int p = threadIdx.x, ri = p / HT, h = blockIdx.y * HT + p % HT;
+        const bool ok = ri < tile_rows && h < heads;
+        const int pos = ok ? positions[row0 + ri] : 0;
+        pair_row[p] = ok ? row0 + ri : -1;
+        pair_pos[p] = pos;
+        pair_lo[p] = window > 0 ? max(0, pos - window + 1) : 0;
+        row_m[p] = -INFINITY;
+        row_l[p] = 0.0f;
+    }
+    for (int i = threadIdx.x; i < 16 * W; i += TILE_THREADS) {
+        const int p = i / W, e = i % W, ri = p / HT, h = blockIdx.y * HT + p % HT;
+        const float x = (ri < tile_rows && h < heads) ? qk[((size_t)(row0 + ri) * heads + h) * W + e] : 0.0f;
+        __nv_bfloat16 a, b, c;
+        split3(x, a, b, c);
+        qs[(size_t)(0 * 16 + p) * WS + e] = a;
+        qs[(size_t)(1 * 16 + p) * WS + e] = b;
+        qs[(size_t)(2 * 16 + p) * WS + e] = c;
+    }
+    const int per_row = W / 8;                      // 16-byte pieces a key has
+    auto issue = [&](int t0, int which) {
+        const uint32_t base = (uint32_t)__cvta_generic_to_shared(keys + (size_t)which * TC_KT * WS);
+        for (int c = threadIdx.x; c < TC_KT * per_row; c += TILE_THREADS) {
+            const int key = c / per_row, piece = c % per_row, t = t0 + key;
+            const bool real = t < end;
+            const __nv_bfloat16* src = cache;
+            if (real) src = cache + ((size_t)table[t / page_size] * page_size + t % page_size) * W + piece * 8;
+            cp_async_16(base + (uint32_t)(key * WS + piece * 8) * 2, src, real);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nb][i] = 0.0f;
+
+    const int n_tiles = end > begin ? (end - begin + TC_KT - 1) / TC_KT : 0;
+    if (n_tiles > 0) issue(begin, 0);
+    const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(qs);
+    const uint32_t ps_addr = (uint32_t)__cvta_generic_to_shared(ps);
+    for (int it = 0; it < n_tiles; ++it) {
+        const int t0 = begin + it * TC_KT;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                             // tile `it` has landed; everyone is done with the other buffer
+        if (it + 1 < n_tiles) issue(t0 + TC_KT, (it + 1) & 1);
+        const uint32_t kaddr = (uint32_t)__cvta_generic_to_shared(keys + (size_t)(it & 1) * TC_KT * WS);
+        // ---- scores: this warp's 8 keys
+        {
+            float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const int n0 = warp * 8;
+            for (int k0 = 0; k0 < W; k0 += 32) {
+                uint32_t b0, b1, b2, b3;         // (b0, b1): columns k0 .. k0 + 15; (b2, b3): the next sixteen
+                attn::ldmatrix_x4(kaddr + (uint32_t)((n0 + (lane & 7)) * WS + k0 + (lane >> 3) * 8) * 2, b0, b1, b2, b3);
+                // The instruction's own additions are cut off, not rounded, at the size of its accumulator: each 32
+                // columns start from nothing and join the score by a rounded addition, the small parts first.
+                float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int sp = 2; sp >= 0; --sp) {
+                    uint32_t a[4];
+                    attn::ldmatrix_x4(qs_addr + (uint32_t)((sp * 16 + (lane & 15)) * WS + k0 + (lane >> 4) * 8) * 2, a[0], a[1], a[2], a[3]);
+                    attn::mma_16816(t, a, b0, b1);
+                    attn::ldmatrix_x4(qs_addr + (uint32_t)((sp * 16 + (lane & 15)) * WS + k0 + 16 + (lane >> 4) * 8) * 2, a[0], a[1], a[2], a[3]);
+                    attn::mma_16816(t, a, b2, b3);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sacc[i] += t[i];
+            }
+            ss[g * TC_SS + n0 + c2] = sacc[0];
+            ss[g * TC_SS + n0 + c2 + 1] = sacc[1];
+            ss[(g + 8) * TC_SS + n0 + c2] = sacc[2];
+            ss[(g + 8) * TC_SS + n0 + c2 + 1] = sacc[3];
+        }
+        __syncthreads();
+        // ---- weights: pairs 2 * warp and 2 * warp + 1, two keys a lane
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int p = 2 * warp + u;
+            const bool ok = pair_row[p] >= 0;
+            const int plo = pair_lo[p], ppos = pair_pos[p];
+            float sv[2];
+            bool valid[2];
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int t = t0 + lane + 32 * x;
+                valid[x] = ok && t < end && t >= plo && t <= ppos;
+                sv[x] = valid[x] ? ss[p * TC_SS + lane + 32 * x] : -INFINITY;
+            }
+            const float m_old = row_m[p];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(sv[0], sv[1])));
+            const float corr = m_new == -INFINITY ? 1.0f : expf(m_old - m_new);
+            float psum = 0.0f;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const float pv = valid[x] ? expf(sv[x] - m_new) : 0.0f;
+                psum += pv;
+                __nv_bfloat16 a, b, c;
+                split3(pv, a, b, c);
+                ps[(0 * 16 + p) * TC_PS + lane + 32 * x] = a;
+                ps[(1 * 16 + p) * TC_PS + lane + 32 * x] = b;
+                ps[(2 * 16 + p) * TC_PS + lane + 32 * x] = c;
+            }
+            psum = warp_sum(psum);
+            __syncwarp();
+            if (lane == 0) {
+                row_m[p] = m_new;
+                row_l[p] = row_l[p] * corr + psum;
+                row_c[p] = corr;
+            }
+        }
+        __syncthreads();
+        // ---- values: this warp's C / 8 columns
+        {
+            const float ca = row_c[g], cb = row_c[g + 8];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                o[nb][0] *= ca;
+                o[nb][1] *= ca;
+                o[nb][2] *= cb;
+                o[nb][3] *= cb;
+            }
+            const int col0 = warp * NB * 8;
+#pragma unroll
+            for (int ks = 0; ks < TC_KT / 16; ++ks) {
+                uint32_t a[3][4];
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp)
+                    attn::ldmatrix_x4(ps_addr + (uint32_t)((sp * 16 + (lane & 15)) * TC_PS + ks * 16 + (lane >> 4) * 8) * 2,
+                                      a[sp][0], a[sp][1], a[sp][2], a[sp][3]);
+                const int key = ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int nb = 0; nb < NB; nb += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    attn::ldmatrix_x4_trans(kaddr + (uint32_t)(key * WS + col0 + nb * 8 + (lane >> 4) * 8) * 2, b0, b1, b2, b3);
+#pragma unroll
+                    for (int sp = 0; sp < 3; ++sp) {
+                        attn::mma_16816(o[nb], a[sp], b0, b1);
+                        attn::mma_16816(o[nb + 1], a[sp], b2, b3);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // ---- the range's partial result: the weighted sum of latents, the maximum, the sum
+    const int col0 = warp * NB * 8;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int p = g + 8 * half;
+        const int row = pair_row[p];
+        if (row < 0) continue;
+        const int h = blockIdx.y * HT + p % HT;
+        float* dst = part + (((size_t)row * heads + h) * splits + blockIdx.z) * (C + 2);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            dst[col0 + nb * 8 + c2] = o[nb][2 * half];
+            dst[col0 + nb * 8 + c2 + 1] = o[nb][2 * half + 1];
+        }
+    }
+    if (threadIdx.x < 16 && pair_row[threadIdx.x] >= 0) {
+        const int p = threadIdx.x, h = blockIdx.y * HT + p % HT;
+        float* dst = part + (((size_t)pair_row[p] * heads + h) * splits + blockIdx.z) * (C + 2);
+        dst[C] = row_m[p];
+        dst[C + 1] = row_l[p];
+    }
+}
+
 template <typename KVT>
 int launch_scores(int plp, dim3 grid, size_t smem, cudaStream_t stream, const float* qk, const void* cache, float* part,
                   const int* tiles, const int* row_request, const int* positions, const int* block_tables, int table_stride,
@@ -594,11 +825,11 @@ LLMX_EXPORT int llmx_latent_query(const float* q, int q_stride, const void* w_uk
 }
 
 // `tiles` (device, int32 [n_tiles, 2]): first row and number of rows (at most the tile shape's) of every row tile, rows
-// of one request each; `splits`: ranges the keys of a tile are cut into.
+// of one request each; `splits`: ranges the keys of a tile are cut into; `plain_cores`: never the tensor-core form.
 LLMX_EXPORT int llmx_latent_scores(const float* qk, const void* cache, int cache_dtype, float* part, const int* tiles,
                                    int n_tiles, int splits, const int* row_request, const int* positions,
                                    const int* block_tables, int table_stride, int heads, int C, int R, int page_size,
-                                   int window, cudaStream_t stream) {
+                                   int window, int plain_cores, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (heads <= 0 || R < 0 || C <= 0 || page_size <= 0 || splits <= 0 || splits > 65535) return LLMX_ERR_BAD_ARGUMENT;
     const int W = C + R, Wp = (W + 1) & ~1;
@@ -608,6 +839,21 @@ LLMX_EXPORT int llmx_latent_scores(const float* qk, const void* cache, int cache
     const dim3 grid(n_tiles, (heads + HT - 1) / HT, splits);
     const size_t smem = (size_t)2 * 64 * Wp;          // two tiles of 64 / sizeof(element) keys
     if (smem > 200 * 1024) return LLMX_ERR_UNSUPPORTED;
+    if (cache_dtype == LLMX_BF16 && !plain_cores && W % 32 == 0 && (C == 128 || C == 256 || C == 512) && tc_smem_bytes(W) <= 220 * 1024) {
+        const size_t tsm = tc_smem_bytes(W);
+#define LLMX_TC(NB)                                                                                                       \
+        do {                                                                                                              \
+            cudaFuncSetAttribute(latent_scores_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm);     \
+            launch_kernel(latent_scores_tc_kernel<NB>, grid, dim3(TILE_THREADS), tsm, stream, qk, (const __nv_bfloat16*)cache, \
+                          part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits,     \
+                          page_size, window);                                                                             \
+        } while (0)
+        if (C == 128) LLMX_TC(2);
+        else if (C == 256) LLMX_TC(4);
+        else LLMX_TC(8);
+#undef LLMX_TC
+        return launch_status();
+    }
     if (cache_dtype == LLMX_BF16)
         return launch_scores<__nv_bfloat16>(plp, grid, smem, stream, qk, cache, part, tiles, row_request, positions, block_tables, table_stride, heads, C, R, HT, splits, page_size, window);
     if (cache_dtype == LLMX_F32)

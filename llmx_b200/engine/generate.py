@@ -85,7 +85,7 @@ class LLM:
         width = 2 if dtype in ("bfloat16", "bf16") else 4
         for spec in model.cache_entry_specs():
             if hasattr(spec, "kv_heads"):
-                per_token += 2 * spec.kv_heads * spec.head_dim * width
+                per_token += getattr(spec, "planes", 2) * spec.kv_heads * spec.head_dim * width
         free, _ = torch.cuda.mem_get_info(torch.device(device))
         by_memory = (free // 3) // max(per_token, 1)
         tokens = int(min(model.max_positions, by_memory))

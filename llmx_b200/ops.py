@@ -108,7 +108,7 @@ _SIGNATURES = {
     ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
     ("latent_attention", "llmx_latent_query"): [_p, _i, _p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _p],
-    ("latent_attention", "llmx_latent_scores"): [_p, _p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    ("latent_attention", "llmx_latent_scores"): [_p, _p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_merge"): [_p, _p, _i, _p, _i, _i, _i, _i, _i, _p],
     ("gemm_plain", "llmx_gemm_plain"): [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p],
     ("attention_plain", "llmx_attention_plain"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
@@ -488,10 +488,12 @@ def latent_tile_shape(heads: int):
 def latent_attention_tiled(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,
                            freq: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
                            tiles: torch.Tensor, n_tiles: int, splits: int, heads: int, key_dim: int, rot: int, value_dim: int,
-                           latent: int, page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+                           latent: int, page_size: int, window: Optional[int], scale: float, plain_cores: bool = False) -> torch.Tensor:
     """`latent_attention` in its tiled form (csrc/latent_attention.cu): `tiles` int32 [n_tiles, 2] on the device, the
     first row and the row count of every tile (rows of one request, at most `latent_tile_shape`'s); `splits` ranges
-    of a tile's keys run as blocks of their own and are merged."""
+    of a tile's keys run as blocks of their own and are merged.  With a bfloat16 cache and a latent of 128, 256 or 512
+    values the scores run on the tensor cores, 32-bit factors as sums of three bfloat16 values; `plain_cores` keeps
+    them on the CUDA cores."""
     _cuda(q, cache, w_uk, w_uv, out, freq, row_request, positions, block_tables, tiles)
     rows = q.shape[0]
     _need(q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot), "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
@@ -509,7 +511,7 @@ def latent_attention_tiled(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Ten
     _check(_fn("latent_attention", "llmx_latent_scores")(_ptr(qk), _ptr(cache), _code(cache), _ptr(part), _ptr(tiles), int(n_tiles),
                                                          int(splits), _ptr(row_request), _ptr(positions), _ptr(block_tables),
                                                          block_tables.shape[1], heads, latent, rot, page_size, int(window or 0),
-                                                         _stream()), "latent_scores")
+                                                         1 if plain_cores else 0, _stream()), "latent_scores")
     _check(_fn("latent_attention", "llmx_latent_merge")(_ptr(part), _ptr(w_uv), _code(w_uv), _ptr(out), rows, heads, value_dim, latent,
                                                         int(splits), _stream()), "latent_merge")
     return out

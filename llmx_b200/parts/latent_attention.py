@@ -50,6 +50,7 @@ class LatentAttention(Part):
         self.q_width = self.heads * (self.key_dim + self.rot_dim)
         self.v_width = self.heads * self.value_dim
         self.freq: Optional[torch.Tensor] = None
+        self.plain_cores = False      # True: the tiled scores stay on the CUDA cores also where the tensor-core form would run
 
     def cache_spec(self):
         return KVSpec(1, self.kv_rank + self.rot_dim, self.window, planes=1)
@@ -115,7 +116,7 @@ class LatentAttention(Part):
             host_tiles, splits = self._tiling(step.host_row_count, step.max_context)
             ops.latent_attention_tiled(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions,
                                        group.block_tables, tiles, len(host_tiles), splits, self.heads, self.key_dim, self.rot_dim,
-                                       self.value_dim, self.kv_rank, group.page_size, self.window, self.scale)
+                                       self.value_dim, self.kv_rank, group.page_size, self.window, self.scale, plain_cores=self.plain_cores)
         else:
             # One block per (row, head): the schedule follows the sizes alone (an invariant path, or a step without a plan).
             ops.latent_attention(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions, group.block_tables,

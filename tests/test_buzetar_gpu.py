@@ -263,6 +263,37 @@ def test_a_token_is_seen_exactly_while_the_window_holds_it(tmp_path, window, pag
             assert np.array_equal(a[:j], b[:j])
 
 
+@pytest.mark.parametrize("kv_rank,rot_dim,heads,window", [(128, 32, 3, 40), (256, 64, 16, None), (512, 64, 5, 150)])
+@pytest.mark.parametrize("sharpen,tol", [(0.25, 5e-5), (2.0, 5e-4)])
+def test_tensor_core_scores_equal_the_cuda_core_scores(tmp_path, kv_rank, rot_dim, heads, window, sharpen, tol):
+    """Latents of 128, 256 and 512 values in a bfloat16 cache: the scores step on the tensor cores (32-bit factors as
+    sums of three bfloat16 values) against the same step on the CUDA cores, over the same cache, under every cutting:
+    whole prompts, portions that cut windows and tiles, single tokens after long histories (key ranges).  With flat
+    scores the two agree as two orders of 32-bit sums do; with scores of tens, the tensor core's cut-off additions show
+    in the exponentials (an absolute error of a score is a relative error of its weight), far below what a key at the
+    wrong place or a lost row would do."""
+    from llmx_b200.engine import Engine, EngineOptions
+    cfg = config([latent(heads=heads, dim=24, rot_dim=rot_dim, vdim=16, q_rank=40, kv_rank=kv_rank, window=window, scale=0.2),
+                  lightning(), latent(heads=2, dim=16, rot_dim=rot_dim, vdim=24, q_rank=32, kv_rank=kv_rank, window=window, rot_dims=rot_dim // 2, mlp=None)])
+    make_folder(str(tmp_path), cfg, seed=21, sharpen=sharpen)
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab"], n, seed=70 + i) for i, n in enumerate([330, 3, 77, 200, 1, 64])}
+    for make in CUTTINGS:
+        steps = make(requests)
+        got = []
+        for plain_cores in (False, True):
+            engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype="float32", kv_dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps),
+                                                                  page_size=16, max_requests=4))
+            for block in engine.model.blocks:
+                if hasattr(block.mixer, "plain_cores"):
+                    block.mixer.plain_cores = plain_cores
+            got.append(helpers.run_trace(engine, steps))
+            engine.cache.check()
+        scale = max(float(np.abs(r).max()) for r in got[1].values())
+        worst = max(float(np.abs(got[0][k] - got[1][k]).max()) for k in got[1])
+        assert len(got[0]) == len(got[1]) == sum(len(v) for v in requests.values())
+        assert np.isfinite(worst) and worst <= tol * scale, (make.__name__, worst, scale)
+
+
 def test_far_keys_without_a_window(tmp_path):
     """Attention without a window over hundreds of keys across many pages: sharpened so that single far keys decide."""
     cfg = config([latent(window=None, rot_dims=4), lightning(decay=(1.0, 0.999, 0.99))])

@@ -216,27 +216,31 @@ latent_query_kernel(const float* __restrict__ q, int q_stride, const WT* __restr
         qraw[i] = r < n ? q[(size_t)(r0 + r) * q_stride + (size_t)h * DR + i % DR] : 0.0f;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n * (R / 2); i += blockDim.x) {
-        const int r = i / (R / 2), k = i % (R / 2);
-        const float a = qraw[r * DR + D + 2 * k], b = qraw[r * DR + D + 2 * k + 1];
-        float ra = a, rb = b;
-        if (k < rot_pairs) {
-            float sn, cs;
-            sincosf((float)positions[r0 + r] * freq[k], &sn, &cs);
-            ra = a * cs - b * sn;
-            rb = b * cs + a * sn;
+    if (blockIdx.z == 0) {
+        for (int i = threadIdx.x; i < n * (R / 2); i += blockDim.x) {
+            const int r = i / (R / 2), k = i % (R / 2);
+            const float a = qraw[r * DR + D + 2 * k], b = qraw[r * DR + D + 2 * k + 1];
+            float ra = a, rb = b;
+            if (k < rot_pairs) {
+                float sn, cs;
+                sincosf((float)positions[r0 + r] * freq[k], &sn, &cs);
+                ra = a * cs - b * sn;
+                rb = b * cs + a * sn;
+            }
+            float* dst = qk + ((size_t)(r0 + r) * heads + h) * (C + R) + C;
+            dst[2 * k] = ra * scale;
+            dst[2 * k + 1] = rb * scale;
         }
-        float* dst = qk + ((size_t)(r0 + r) * heads + h) * (C + R) + C;
-        dst[2 * k] = ra * scale;
-        dst[2 * k + 1] = rb * scale;
+        if ((R & 1) && (int)threadIdx.x < n)
+            qk[((size_t)(r0 + threadIdx.x) * heads + h) * (C + R) + C + R - 1] = qraw[threadIdx.x * DR + DR - 1] * scale;
     }
-    if ((R & 1) && (int)threadIdx.x < n)
-        qk[((size_t)(r0 + threadIdx.x) * heads + h) * (C + R) + C + R - 1] = qraw[threadIdx.x * DR + DR - 1] * scale;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int c = blockIdx.z * blockDim.x + threadIdx.x;      // one column of the key map a thread
+    if (c < C) {
         const WT* col = w_uk + (size_t)h * D * C + c;
         float s[ROWS_Q];
 #pragma unroll
         for (int r = 0; r < ROWS_Q; ++r) s[r] = 0.0f;
+#pragma unroll 8
         for (int d = 0; d < D; ++d) {
             const float w = to_float(col[(size_t)d * C]);
 #pragma unroll
@@ -510,7 +514,9 @@ latent_merge_kernel(const float* __restrict__ part, const WT* __restrict__ w_uv,
         }
     }
     __syncthreads();
-    for (int v = warp; v < V; v += 4) {
+    const int v_per = (V + gridDim.z - 1) / gridDim.z;
+    const int v_end = min(V, (int)(blockIdx.z + 1) * v_per);
+    for (int v = blockIdx.z * v_per + warp; v < v_end; v += 4) {
         const WT* wr = w_uv + ((size_t)h * V + v) * C;
         float s[ROWS_Q];
 #pragma unroll
@@ -809,7 +815,7 @@ LLMX_EXPORT int llmx_latent_query(const float* q, int q_stride, const void* w_uk
     const int rq = rows > 64 ? 8 : 1;
     const size_t smem = (size_t)rq * (D + R) * sizeof(float);
     if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
-    const dim3 grid((rows + rq - 1) / rq, heads);
+    const dim3 grid((rows + rq - 1) / rq, heads, (C + 127) / 128);
 #define LLMX_Q(WT, RQ)                                                                                                    \
     launch_kernel(latent_query_kernel<WT, RQ>, grid, dim3(128), smem, stream, q, q_stride, (const WT*)w_uk, qk, freq,      \
                   rot_pairs, positions, rows, heads, D, R, C, scale)
@@ -868,7 +874,7 @@ LLMX_EXPORT int llmx_latent_merge(const float* part, const void* w_uv, int w_dty
     const int rq = rows > 64 ? 8 : 1;
     const size_t smem = (size_t)rq * C * sizeof(float);
     if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
-    const dim3 grid((rows + rq - 1) / rq, heads);
+    const dim3 grid((rows + rq - 1) / rq, heads, rq == 1 ? (V + 15) / 16 : (V + 63) / 64);      // 16 (few rows) or 64 value rows a block
 #define LLMX_M(WT, RQ)                                                                                                    \
     launch_kernel(latent_merge_kernel<WT, RQ>, grid, dim3(128), smem, stream, part, (const WT*)w_uv, (WT*)out, rows,      \
                   heads, V, C, splits)

@@ -24,10 +24,9 @@
 namespace {
 constexpr int REC_THREADS = 128;
 
-// LANES threads share one column of the state, each holding PER of its D values (D <= LANES * PER); a block of 128
-// threads owns 128 / LANES columns of one head.  Few lanes a column (8) make short sums over the lanes and suit steps of
-// a row or a few; a whole warp a column (32) makes four times as many threads and short chains of multiply-adds, which
-// is what a long run of rows, one after the other, waits on.  A row's q, k, v and gates are fetched one row ahead.
+// The form for steps of a row or a few: LANES (8) threads share one column of the state, each holding PER of its D
+// values (D <= LANES * PER), so a sum over the lanes is three shuffle steps; a block of 128 threads owns 16 columns of
+// one head.  A row's q, k, v and gates are fetched one row ahead.
 template <int PER, int LANES, bool DELTA>
 __global__ void __launch_bounds__(REC_THREADS)
 recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int q_stride,
@@ -116,6 +115,112 @@ recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     }
 }
 
+// The wide form for long runs of rows: a warp a column, eight columns of one head a block, and the rows' q, k, v and
+// gates brought to shared memory sixteen rows at a time by cp.async (the next sixteen in flight meanwhile), so that
+// a row waits for shared memory and for the row before it, not for the L2 cache.
+constexpr int WIDE_THREADS = 256, WIDE_COLS = 8, WIDE_CH = 16;
+
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int PER, bool DELTA>
+__global__ void __launch_bounds__(WIDE_THREADS)
+recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int q_stride,
+                       int k_stride, int v_stride, const float* __restrict__ decay, const float* __restrict__ gate,
+                       const float* __restrict__ beta, int gate_stride, float* __restrict__ state, long long slot_floats,
+                       const int* __restrict__ row_start, const int* __restrict__ row_count,
+                       const int* __restrict__ history, const int* __restrict__ slot_in,
+                       const int* __restrict__ slot_out, float* __restrict__ out, int heads, int qk_heads, int D, int V) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float stage[];                 // [2][WIDE_CH][row_floats]: q (D), k (D), v (8 columns), gate, beta
+    const int row_floats = 2 * D + WIDE_COLS + 2;
+    const int r = blockIdx.x;
+    const int blocks_per_head = (V + WIDE_COLS - 1) / WIDE_COLS;
+    const int h = blockIdx.y / blocks_per_head;
+    const int first_col = (blockIdx.y % blocks_per_head) * WIDE_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = first_col + warp;
+    const int n = row_count[r];
+    if (n <= 0) return;
+    const bool live = col < V;
+    const int j = live ? col : V - 1;
+    const int a0 = row_start[r];
+    const int hq = h / (heads / qk_heads);
+    float S[PER];
+    const float* sin_ = state + (size_t)slot_in[r] * slot_floats + ((size_t)h * V + j) * D;
+    const bool fresh = history[r] == 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + i * 32;
+        S[i] = (!fresh && d < D) ? sin_[d] : 0.0f;
+    }
+    const float dec = DELTA ? 0.0f : decay[h];
+    auto issue = [&](int chunk, int which) {
+        float* buf = stage + (size_t)which * WIDE_CH * row_floats;
+        const int t0 = chunk * WIDE_CH, rows = min(WIDE_CH, n - t0);
+        for (int i = threadIdx.x; i < rows * row_floats; i += WIDE_THREADS) {
+            const int t = i / row_floats, e = i % row_floats;
+            const size_t row = (size_t)(a0 + t0 + t);
+            const float* src;
+            if (e < D) src = q + row * q_stride + (size_t)hq * D + e;
+            else if (e < 2 * D) src = k + row * k_stride + (size_t)hq * D + (e - D);
+            else if (e < 2 * D + WIDE_COLS) src = v + row * v_stride + (size_t)h * V + min(first_col + e - 2 * D, V - 1);
+            else if (!DELTA) continue;
+            else if (e == 2 * D + WIDE_COLS) src = gate + row * gate_stride + h;
+            else src = beta + row * gate_stride + h;
+            cp_async_4(buf + i, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int chunks = (n + WIDE_CH - 1) / WIDE_CH;
+    issue(0, 0);
+    for (int c = 0; c < chunks; ++c) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                             // chunk c has landed; everyone has left the other buffer
+        if (c + 1 < chunks) issue(c + 1, (c + 1) & 1);
+        const float* buf = stage + (size_t)(c & 1) * WIDE_CH * row_floats;
+        const int rows = min(WIDE_CH, n - c * WIDE_CH);
+        for (int t = 0; t < rows; ++t) {
+            const float* rowp = buf + (size_t)t * row_floats;
+            float kk[PER], qq[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + i * 32;
+                qq[i] = d < D ? rowp[d] : 0.0f;
+                kk[i] = d < D ? rowp[D + d] : 0.0f;
+            }
+            float u = rowp[2 * D + warp];
+            float a = dec;
+            if (DELTA) {
+                a = rowp[2 * D + WIDE_COLS];
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PER; ++i) dot = fmaf(S[i], kk[i], dot);
+                dot = warp_sum(dot);
+                u = rowp[2 * D + WIDE_COLS + 1] * (u - a * dot);
+            }
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                S[i] = fmaf(a, S[i], kk[i] * u);
+                acc = fmaf(S[i], qq[i], acc);
+            }
+            acc = warp_sum(acc);
+            if (live && lane == 0) out[(size_t)(a0 + c * WIDE_CH + t) * ((size_t)heads * V) + (size_t)h * V + j] = acc;
+        }
+    }
+    if (live) {
+        float* sout = state + (size_t)slot_out[r] * slot_floats + ((size_t)h * V + j) * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < D) sout[d] = S[i];
+        }
+    }
+}
+
 // One block per row (conv, activation, unit vectors, gates) and, after those, one block per request (the inputs the
 // next step's convolution will need).
 __global__ void __launch_bounds__(256)
@@ -198,10 +303,23 @@ int launch_recurrence(int D, bool wide, int requests, cudaStream_t stream, const
         return launch_status();                                                                                           \
     } while (0)
     if (wide) {
-        if (D <= 32) LLMX_REC(1, 32);
-        if (D <= 64) LLMX_REC(2, 32);
-        if (D <= 128) LLMX_REC(4, 32);
-        if (D <= 256) LLMX_REC(8, 32);
+#define LLMX_WIDE(P)                                                                                                      \
+    do {                                                                                                                  \
+        const long long by = (long long)heads * ((V + WIDE_COLS - 1) / WIDE_COLS);                                        \
+        if (by > 65535) return LLMX_ERR_UNSUPPORTED;                                                                      \
+        const size_t smem = (size_t)2 * WIDE_CH * (2 * D + WIDE_COLS + 2) * sizeof(float);                                \
+        if (smem > 48 * 1024)                                                                                             \
+            cudaFuncSetAttribute(recurrence_wide_kernel<P, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_kernel(recurrence_wide_kernel<P, DELTA>, dim3(requests, (unsigned)by), dim3(WIDE_THREADS), smem, stream, q, \
+                      k, v, q_stride, k_stride, v_stride, decay, gate, beta, gate_stride, state, slot_floats, row_start,  \
+                      row_count, history, slot_in, slot_out, out, heads, qk_heads, D, V);                                \
+        return launch_status();                                                                                           \
+    } while (0)
+        if (D <= 32) LLMX_WIDE(1);
+        if (D <= 64) LLMX_WIDE(2);
+        if (D <= 128) LLMX_WIDE(4);
+        if (D <= 256) LLMX_WIDE(8);
+#undef LLMX_WIDE
     } else {
         if (D <= 16) LLMX_REC(2, 8);
         if (D <= 32) LLMX_REC(4, 8);

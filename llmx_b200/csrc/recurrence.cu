@@ -124,6 +124,26 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+__device__ __forceinline__ void cp_async_16f(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// A lane holds the PER neighbouring values d = PER * lane .. of its column, so that a row's q and k are one
+// 16-byte read each from shared memory when PER is 4.
+template <int PER>
+__device__ __forceinline__ void read_run(const float* p, int lane, int D, float (&out)[PER]) {
+    if (PER == 4 && D % 4 == 0) {
+        const float4 x = lane * 4 < D ? *reinterpret_cast<const float4*>(p + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        out[0] = x.x;
+        out[1] = x.y;
+        out[2] = x.z;
+        out[3] = x.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) out[i] = lane * PER + i < D ? p[lane * PER + i] : 0.0f;
+    }
+}
+
 template <int PER, bool DELTA>
 __global__ void __launch_bounds__(WIDE_THREADS)
 recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int q_stride,
@@ -134,8 +154,9 @@ recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k,
                        const int* __restrict__ slot_out, float* __restrict__ out, int heads, int qk_heads, int D, int V) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float stage[];                 // [2][WIDE_CH][row_floats]: q (D), k (D), v (8 columns), gate, beta
-    const int row_floats = 2 * D + WIDE_COLS + 2;
+    extern __shared__ __align__(16) float stage[];   // [2][WIDE_CH][row_floats]: q (Dp), k (Dp), v (8 columns), gate, beta, pad
+    const int Dp = PER * 32;                         // a row's q and k padded to the lanes' runs (the pad is never written: zeros are read by the guard)
+    const int row_floats = 2 * Dp + WIDE_COLS + 4;   // a multiple of 4: every row starts on 16 bytes
     const int r = blockIdx.x;
     const int blocks_per_head = (V + WIDE_COLS - 1) / WIDE_COLS;
     const int h = blockIdx.y / blocks_per_head;
@@ -153,24 +174,46 @@ recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k,
     const bool fresh = history[r] == 0;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-        const int d = lane + i * 32;
+        const int d = lane * PER + i;
         S[i] = (!fresh && d < D) ? sin_[d] : 0.0f;
     }
     const float dec = DELTA ? 0.0f : decay[h];
+    // What this thread copies of every chunk is the same from chunk to chunk, so its places are worked out once:
+    // pieces of 16 bytes of q and k when rows allow it (else single values), and one of the chunk's small values.
+    const bool vec = D % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0;
+    const int unit = vec ? 4 : 1;
+    const int per_row = 2 * (D / unit);              // copies a row's q and k take
+    constexpr int MAX_COPIES = 2 * PER * 32 * WIDE_CH / WIDE_THREADS;      // at most, with single values
+    const int small_t = threadIdx.x / (WIDE_COLS + 2), small_e = threadIdx.x % (WIDE_COLS + 2);
     auto issue = [&](int chunk, int which) {
         float* buf = stage + (size_t)which * WIDE_CH * row_floats;
         const int t0 = chunk * WIDE_CH, rows = min(WIDE_CH, n - t0);
-        for (int i = threadIdx.x; i < rows * row_floats; i += WIDE_THREADS) {
-            const int t = i / row_floats, e = i % row_floats;
+        const int copies = rows * per_row;
+        int p = threadIdx.x, t = p / per_row, e = p % per_row;
+        const int dt = WIDE_THREADS / per_row, de = WIDE_THREADS % per_row;
+#pragma unroll 4
+        for (int i = 0; i < MAX_COPIES; ++i) {
+            if (p >= copies) break;
             const size_t row = (size_t)(a0 + t0 + t);
-            const float* src;
-            if (e < D) src = q + row * q_stride + (size_t)hq * D + e;
-            else if (e < 2 * D) src = k + row * k_stride + (size_t)hq * D + (e - D);
-            else if (e < 2 * D + WIDE_COLS) src = v + row * v_stride + (size_t)h * V + min(first_col + e - 2 * D, V - 1);
-            else if (!DELTA) continue;
-            else if (e == 2 * D + WIDE_COLS) src = gate + row * gate_stride + h;
-            else src = beta + row * gate_stride + h;
-            cp_async_4(buf + i, src);
+            const bool is_k = e >= D / unit;
+            const int off = (is_k ? e - D / unit : e) * unit;
+            const float* src = is_k ? k + row * k_stride + (size_t)hq * D + off : q + row * q_stride + (size_t)hq * D + off;
+            float* dst = buf + (size_t)t * row_floats + (is_k ? Dp : 0) + off;
+            if (vec) cp_async_16f(dst, src);
+            else cp_async_4(dst, src);
+            p += WIDE_THREADS;
+            t += dt;
+            e += de;
+            if (e >= per_row) {
+                e -= per_row;
+                ++t;
+            }
+        }
+        if (small_t < rows && (DELTA || small_e < WIDE_COLS)) {
+            const size_t row = (size_t)(a0 + t0 + small_t);
+            const float* src = small_e < WIDE_COLS ? v + row * v_stride + (size_t)h * V + min(first_col + small_e, V - 1)
+                             : small_e == WIDE_COLS ? gate + row * gate_stride + h : beta + row * gate_stride + h;
+            cp_async_4(buf + (size_t)small_t * row_floats + 2 * Dp + small_e, src);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -185,21 +228,17 @@ recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k,
         for (int t = 0; t < rows; ++t) {
             const float* rowp = buf + (size_t)t * row_floats;
             float kk[PER], qq[PER];
-#pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int d = lane + i * 32;
-                qq[i] = d < D ? rowp[d] : 0.0f;
-                kk[i] = d < D ? rowp[D + d] : 0.0f;
-            }
-            float u = rowp[2 * D + warp];
+            read_run<PER>(rowp, lane, D, qq);
+            read_run<PER>(rowp + Dp, lane, D, kk);
+            float u = rowp[2 * Dp + warp];
             float a = dec;
             if (DELTA) {
-                a = rowp[2 * D + WIDE_COLS];
+                a = rowp[2 * Dp + WIDE_COLS];
                 float dot = 0.0f;
 #pragma unroll
                 for (int i = 0; i < PER; ++i) dot = fmaf(S[i], kk[i], dot);
                 dot = warp_sum(dot);
-                u = rowp[2 * D + WIDE_COLS + 1] * (u - a * dot);
+                u = rowp[2 * Dp + WIDE_COLS + 1] * (u - a * dot);
             }
             float acc = 0.0f;
 #pragma unroll
@@ -215,7 +254,7 @@ recurrence_wide_kernel(const float* __restrict__ q, const float* __restrict__ k,
         float* sout = state + (size_t)slot_out[r] * slot_floats + ((size_t)h * V + j) * D;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            const int d = lane + i * 32;
+            const int d = lane * PER + i;
             if (d < D) sout[d] = S[i];
         }
     }
@@ -307,7 +346,7 @@ int launch_recurrence(int D, bool wide, int requests, cudaStream_t stream, const
     do {                                                                                                                  \
         const long long by = (long long)heads * ((V + WIDE_COLS - 1) / WIDE_COLS);                                        \
         if (by > 65535) return LLMX_ERR_UNSUPPORTED;                                                                      \
-        const size_t smem = (size_t)2 * WIDE_CH * (2 * D + WIDE_COLS + 2) * sizeof(float);                                \
+        const size_t smem = (size_t)2 * WIDE_CH * (2 * P * 32 + WIDE_COLS + 4) * sizeof(float);                                \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(recurrence_wide_kernel<P, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_kernel(recurrence_wide_kernel<P, DELTA>, dim3(requests, (unsigned)by), dim3(WIDE_THREADS), smem, stream, q, \

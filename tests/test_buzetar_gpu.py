@@ -127,6 +127,9 @@ ONE_LAYER = {
     "delta": delta(),
     "delta_one_tap_group_of_three": delta(heads=6, kv_heads=2, dim=12, vdim=16, conv=1, mlp=None),
     "delta_long_filter": delta(heads=1, kv_heads=1, dim=32, vdim=8, conv=6),
+    "delta_rows_off_16_bytes": delta(heads=3, kv_heads=3, dim=8, vdim=5, conv=2),          # q/k widths of 4s in rows that are not
+    "latent_18_heads": latent(heads=18, dim=8, rot_dim=4, vdim=6, q_rank=20, kv_rank=24, window=30),      # two groups of heads a tile
+    "lightning_wide_heads": lightning(heads=2, dim=160, vdim=24, decay=(0.99, 0.9)),       # more than four values a lane
 }
 
 
@@ -263,7 +266,7 @@ def test_a_token_is_seen_exactly_while_the_window_holds_it(tmp_path, window, pag
             assert np.array_equal(a[:j], b[:j])
 
 
-@pytest.mark.parametrize("kv_rank,rot_dim,heads,window", [(128, 32, 3, 40), (256, 64, 16, None), (512, 64, 5, 150)])
+@pytest.mark.parametrize("kv_rank,rot_dim,heads,window", [(128, 32, 3, 40), (256, 64, 20, None), (512, 64, 5, 150)])
 @pytest.mark.parametrize("sharpen,tol", [(0.25, 5e-5), (2.0, 5e-4)])
 def test_tensor_core_scores_equal_the_cuda_core_scores(tmp_path, kv_rank, rot_dim, heads, window, sharpen, tol):
     """Latents of 128, 256 and 512 values in a bfloat16 cache: the scores step on the tensor cores (32-bit factors as

@@ -356,6 +356,41 @@ def test_greedy_generation_through_the_scheduler(tmp_path, dtype):
     assert llm.engine.cache.state_slots.free_slots == llm.engine.cache.state_slots.num_slots
 
 
+def test_recorded_steps_equal_plain_steps(tmp_path):
+    """Steps whose shape keeps coming are recorded as CUDA graphs and replayed: the same logits as the plain
+    implementation, portions and decoded tokens, with the tiled attention's plan made for the recording's room."""
+    from llmx_b200.engine import Engine, EngineOptions
+    cfg = MODEL_P
+    w = make_folder(str(tmp_path), cfg, seed=14)
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab"], n, seed=30 + i) for i, n in enumerate([70, 70, 70, 41])}
+    refs = {rid: plain.forward(cfg, w, ids) for rid, ids in requests.items()}
+    steps = helpers.trace_portions(requests, portions=[7, 7, 7, 7, 7, 7, 7, 7, 7, 1, 1, 1, 1, 1, 1, 1])
+    engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype="float32", kv_tokens=256, page_size=16, max_requests=2, record_after=1))
+    assert engine.model.recordable
+    got = helpers.run_trace(engine, steps, record=True)
+    assert len(engine.step_recordings) >= 2          # the portion of seven rows and the single row, at least
+    worst, where = worst_error(got, refs)
+    assert worst <= 1e-4 * max(float(np.abs(r).max()) for r in refs.values()), where
+    engine.cache.check()
+
+
+def test_command_line_generates_from_a_folder(tmp_path):
+    cfg = MODEL_Q
+    w = make_folder(str(tmp_path), cfg, seed=15, dtype=torch.bfloat16)
+    run = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llmx"), "generate", str(tmp_path), "5,17,3,99", "-n", "6", "--temp", "0",
+                          "--ignore-eos", "--dtype", "f32"], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    ids = next(l for l in run.stdout.splitlines() if l.startswith("ids: "))
+    tokens = [int(t) for t in ids[5:].split(",")]
+    assert len(tokens) == 6
+    seq = [5, 17, 3, 99]
+    for t in tokens:
+        logits = plain.forward(cfg, w, seq)[-1]
+        best = int(np.argmax(logits))
+        assert t == best or logits[best] - logits[t] <= 1e-4 * np.abs(logits).max()
+        seq.append(t)
+
+
 def test_trace_run_program(tmp_path):
     cfg = MODEL_Q
     w = make_folder(str(tmp_path / "m"), cfg, seed=12, dtype=torch.bfloat16)

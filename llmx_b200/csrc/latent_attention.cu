@@ -7,8 +7,8 @@
 // and the values are made after the weighted sum: o_h = Wuv_h (sum_t p_t c_t).  Both maps cost D x C and V x C
 // multiply-adds per (row, head), whatever the number of keys, and the cache row is read as it lies.
 //
-// `llmx_latent_write`: per row, RMS norm of the first C values of the down projection's output (weight, eps),
-// rotation of the last R by the row's position, both stored to the row's cache slot.
+// `llmx_latent_write`: per row of the stacked down projections, the query latent's RMS norm (for the product that
+// makes the queries), and the key/value latent's RMS norm and the rotated key part, stored to the row's cache slot.
 // `llmx_latent_attention`: one block per (row, head): rotation of the query's rotated part, the key map, an online
 // softmax over the row's keys lo..p (lo = max(0, p - window + 1), window <= 0: all), warps taking every fourth key
 // in increasing order and merged in warp order, then the value map.  Scores, weights and sums are 32-bit.
@@ -22,18 +22,29 @@
 namespace {
 constexpr int WARPS = 4;
 
-template <typename KVT>
+// A row of the stacked down projections is [query latent (Q) | key/value latent (C) | rotated key part (R)].  One block
+// per row: the query latent's RMS norm (weight wq) goes to `cq` in the type the next product reads; the key/value
+// latent's RMS norm (weight w) and the rotated part go to the row's cache slot (skipped when the slot is negative).
+template <typename KVT, typename QT>
 __global__ void __launch_bounds__(128)
-latent_write_kernel(const float* __restrict__ dkv, int stride, const float* __restrict__ w, float eps,
-                    const float* __restrict__ freq, int rot_pairs, const int* __restrict__ positions,
-                    const int* __restrict__ slots, KVT* __restrict__ cache, int C, int R) {
+latent_write_kernel(const float* __restrict__ down, int stride, int Q, const float* __restrict__ wq, QT* __restrict__ cq,
+                    const float* __restrict__ w, float eps, const float* __restrict__ freq, int rot_pairs,
+                    const int* __restrict__ positions, const int* __restrict__ slots, KVT* __restrict__ cache, int C,
+                    int R) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
     const int row = blockIdx.x;
+    const float* qsrc = down + (size_t)row * stride;
+    if (Q > 0) {
+        float s = 0.0f;
+        for (int i = threadIdx.x; i < Q; i += blockDim.x) s = fmaf(qsrc[i], qsrc[i], s);
+        const float rr = 1.0f / sqrtf(block_sum(s, scratch) / (float)Q + eps);
+        for (int i = threadIdx.x; i < Q; i += blockDim.x) cq[(size_t)row * Q + i] = from_float<QT>(qsrc[i] * (rr * wq[i]));
+    }
     const int slot = slots[row];
     if (slot < 0) return;
-    const float* src = dkv + (size_t)row * stride;
+    const float* src = qsrc + Q;
     KVT* dst = cache + (size_t)slot * (C + R);
     float s = 0.0f;
     for (int i = threadIdx.x; i < C; i += blockDim.x) s = fmaf(src[i], src[i], s);
@@ -889,18 +900,23 @@ LLMX_EXPORT int llmx_latent_merge(const float* part, const void* w_uv, int w_dty
     return launch_status();
 }
 
-// dkv float [rows, stride]: C latent values then R rotated-part values; w float [C]; freq float [rot_pairs];
-// slots[row] = page * page_size + offset (negative: skip the row); cache [pages * page_size, C + R] of `cache_dtype`.
-LLMX_EXPORT int llmx_latent_write(const float* dkv, int stride, const float* w, float eps, const float* freq, int rot_pairs,
-                                  const int* positions, const int* slots, void* cache, int cache_dtype, int rows, int C,
-                                  int R, cudaStream_t stream) {
+// down float [rows, stride]: Q query-latent values, C latent values, R rotated-part values; wq float [Q], w float [C];
+// cq [rows, Q] of `cq_dtype` (Q may be 0: no query latent in the rows); freq float [rot_pairs]; slots[row] = page *
+// page_size + offset (negative: no cache write for the row); cache [pages * page_size, C + R] of `cache_dtype`.
+LLMX_EXPORT int llmx_latent_write(const float* down, int stride, int Q, const float* wq, void* cq, int cq_dtype, const float* w,
+                                  float eps, const float* freq, int rot_pairs, const int* positions, const int* slots,
+                                  void* cache, int cache_dtype, int rows, int C, int R, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (C <= 0 || R < 0 || 2 * rot_pairs > R) return LLMX_ERR_BAD_ARGUMENT;
-    if (cache_dtype == LLMX_BF16)
-        launch_kernel(latent_write_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, dkv, stride, w, eps, freq, rot_pairs, positions, slots, (__nv_bfloat16*)cache, C, R);
-    else if (cache_dtype == LLMX_F32)
-        launch_kernel(latent_write_kernel<float>, dim3(rows), dim3(128), 0, stream, dkv, stride, w, eps, freq, rot_pairs, positions, slots, (float*)cache, C, R);
+    if (C <= 0 || R < 0 || Q < 0 || 2 * rot_pairs > R || stride < Q + C + R) return LLMX_ERR_BAD_ARGUMENT;
+#define LLMX_LW(KVT, QT)                                                                                                  \
+    launch_kernel(latent_write_kernel<KVT, QT>, dim3(rows), dim3(128), 0, stream, down, stride, Q, wq, (QT*)cq, w, eps,   \
+                  freq, rot_pairs, positions, slots, (KVT*)cache, C, R)
+    if (cache_dtype == LLMX_BF16 && cq_dtype == LLMX_BF16) LLMX_LW(__nv_bfloat16, __nv_bfloat16);
+    else if (cache_dtype == LLMX_BF16 && cq_dtype == LLMX_F32) LLMX_LW(__nv_bfloat16, float);
+    else if (cache_dtype == LLMX_F32 && cq_dtype == LLMX_BF16) LLMX_LW(float, __nv_bfloat16);
+    else if (cache_dtype == LLMX_F32 && cq_dtype == LLMX_F32) LLMX_LW(float, float);
     else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_LW
     return launch_status();
 }
 

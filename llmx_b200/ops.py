@@ -104,7 +104,7 @@ _SIGNATURES = {
                                                _p, _p, _i, _i, _i, _i, _i, _i, _p],
     ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p,
                                           ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
-    ("latent_attention", "llmx_latent_write"): [_p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
+    ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
     ("latent_attention", "llmx_latent_query"): [_p, _i, _p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _p],
@@ -438,20 +438,28 @@ def conv_prepare(proj: torch.Tensor, channels: int, q_channels: int, k_channels:
 
 # ---------------------------------------------------------------------------
 # Attention over a cache of latents.
-def latent_write(dkv: torch.Tensor, weight: torch.Tensor, eps: float, freq: torch.Tensor, positions: torch.Tensor,
-                 slots: torch.Tensor, cache: torch.Tensor, latent: int, rot: int) -> None:
-    """cache[slot] = [rmsnorm(dkv[:, :latent]) * weight ; rotate(dkv[:, latent:latent + rot])]; cache [pages, 1, 1, page, latent + rot]."""
-    _cuda(dkv, weight, freq, positions, slots, cache)
-    rows = dkv.shape[0]
-    _need(dkv.dtype == torch.float32 and dkv.dim() == 2 and dkv.shape[1] == latent + rot, "latent_write: down projection float32 [rows, latent + rot]")
+def latent_write(down: torch.Tensor, q_rank: int, q_weight: Optional[torch.Tensor], cq: Optional[torch.Tensor], weight: torch.Tensor,
+                 eps: float, freq: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor, latent: int,
+                 rot: int) -> None:
+    """Rows of the stacked down projections [query latent | key/value latent | rotated key part]:
+    cq = rmsnorm(query latent) * q_weight (in cq's type; `q_rank` 0: the rows hold no query latent), and
+    cache[slot] = [rmsnorm(key/value latent) * weight ; rotate(rotated part)]; cache [pages, 1, 1, page, latent + rot]."""
+    _cuda(down, q_weight, cq, weight, freq, positions, slots, cache)
+    rows = down.shape[0]
+    _need(down.dtype == torch.float32 and down.dim() == 2 and down.shape[1] == q_rank + latent + rot,
+          "latent_write: down projections float32 [rows, q_rank + latent + rot]")
+    if q_rank:
+        _need(q_weight is not None and cq is not None and q_weight.dtype == torch.float32 and q_weight.numel() == q_rank
+              and tuple(cq.shape) == (rows, q_rank), "latent_write: query latent weight [q_rank] and output [rows, q_rank]")
     _need(weight.dtype == torch.float32 and weight.numel() == latent and freq.dtype == torch.float32 and 2 * freq.numel() <= rot,
           "latent_write: weight [latent], frequencies [<= rot / 2]")
     _need(cache.shape[-1] == latent + rot, "latent_write: cache rows do not fit")
     _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= rows and slots.numel() >= rows,
           "latent_write: positions and slots must be int32 per row")
-    _check(_fn("latent_attention", "llmx_latent_write")(_ptr(dkv), dkv.shape[1], _ptr(weight), float(eps), _ptr(freq), freq.numel(),
-                                                        _ptr(positions), _ptr(slots), _ptr(cache), _code(cache), rows, latent, rot,
-                                                        _stream()), "latent_write")
+    _check(_fn("latent_attention", "llmx_latent_write")(_ptr(down), down.shape[1], int(q_rank), _ptr(q_weight), _ptr(cq),
+                                                        _code(cq) if cq is not None else F32, _ptr(weight), float(eps), _ptr(freq),
+                                                        freq.numel(), _ptr(positions), _ptr(slots), _ptr(cache), _code(cache), rows,
+                                                        latent, rot, _stream()), "latent_write")
 
 
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,

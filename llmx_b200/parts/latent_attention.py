@@ -3,7 +3,7 @@
 For the rows of a step, with H heads, D unrotated and R rotated query/key values per head, V value values per head,
 a query latent of `q_rank` and a key/value latent of C = `kv_rank` values:
     cq = RMSNorm(h Wdq^T) * w_dq;   q = cq Wuq^T, per head [D unrotated | R rotated]
-    [c_raw | r_raw] = h Wdkv^T (C + R values);   c = RMSNorm(c_raw) * w_dkv;   r = rotate(r_raw) (one part for all heads)
+    [c_raw | r_raw] = h Wdkv^T (C + R values; one product with Wdq over the stacked weight);   c = RMSNorm(c_raw) * w_dkv;   r = rotate(r_raw) (one part for all heads)
     per head: k = [Wuk_h c | r],  v = Wuv_h c,   s = (q_plain . Wuk_h c + rotate(q_rot) . r) * scale
     o = softmax over the keys lo..p (lo = 0, or p - window + 1 under a sliding window) of s, times v
     residual += o Wo^T
@@ -66,7 +66,8 @@ class LatentAttention(Part):
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
         t = tensors
-        self.dq, self.uq, self.dkv, self.o = (Linear(t[n], precision) for n in ("dq", "uq", "dkv", "o"))
+        self.down = Linear(torch.cat([t["dq"], t["dkv"]], dim=0), precision)      # one product for both latents
+        self.uq, self.o = Linear(t["uq"], precision), Linear(t["o"], precision)
         self.dq_norm = t["dq.norm"].to(torch.float32).contiguous()
         self.dkv_norm = t["dkv.norm"].to(torch.float32).contiguous()
         self.w_uk = t["uk"].to(precision.act).contiguous()
@@ -103,11 +104,10 @@ class LatentAttention(Part):
                 and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
             raise runtime.KernelError("latent attention: rows of the path's type and the mixer's width, a float32 residual")
         group, cache = step.kv(cache_entry)
-        if write_cache:
-            ops.latent_write(self.dkv(h), self.dkv_norm, self.norm_eps, self.freq, step.positions, group.slots, cache,
-                             self.kv_rank, self.rot_dim)
         cq = torch.empty((rows, self.q_rank), dtype=self.precision.act, device=h.device)
-        ops.rmsnorm(self.dq(h), self.dq_norm, self.norm_eps, cq)
+        slots = group.slots if write_cache else torch.full((rows,), -1, dtype=torch.int32, device=h.device)
+        ops.latent_write(self.down(h), self.q_rank, self.dq_norm, cq, self.dkv_norm, self.norm_eps, self.freq, step.positions,
+                         slots, cache, self.kv_rank, self.rot_dim)
         q = self.uq(cq)
         o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
         tiles = None if self.precision.invariant else step.plan_ints(self)

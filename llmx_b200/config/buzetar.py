@@ -110,7 +110,9 @@ def _read_mixer(kind: str, m: Dict[str, Any], where: str):
             raise ConfigError(f"buzetar: {where}.decay must be a list of {heads} numbers (one per head), got {decay!r}")
         return LightningMixer(heads, _int(m, "dim", where), _int(m, "vdim", where), tuple(float(x) for x in decay))
     if kind == "latent_attention":
-        rot = _obj(m, "rot", where)
+        rot = m.get("rot") if m.get("rot_dim") == 0 and not isinstance(m.get("rot"), dict) else _obj(m, "rot", where)
+        if not isinstance(rot, dict):
+            rot = {"base": 10000.0, "dims": 0}          # nothing is rotated: the base is never used
         mask = m.get("mask")
         window = None
         if mask is not None:

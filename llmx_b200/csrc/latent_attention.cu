@@ -551,7 +551,8 @@ latent_merge_kernel(const float* __restrict__ part, const WT* __restrict__ w_uv,
 // as the sum of three bfloat16 values (x = hi + mid + lo, each the rounding of what the ones before left over): the
 // products with the cache's bfloat16 values are exact and are added in 32-bit, so scores and weights keep 32-bit
 // precision although the instruction takes 16-bit operands, at three instructions for one.
-//   scores: warp w makes S[16 pairs, its 8 keys of the tile's 64] = (Qhi + Qmid + Qlo) K^T over C + R
+//   scores: warp w makes S[16 pairs, 16 of the tile's 64 keys] = (Qhi + Qmid + Qlo) K^T over half of C + R; the halves
+//           are added when the weights are made
 //   weights: warp w takes pairs 2w, 2w + 1: mask, running maximum and sum, p = exp(s - m) split three ways
 //   values: warp w owns C / 8 columns of the weighted sum of latents: O = corr O + (Phi + Pmid + Plo) Kc
 // Key tiles come by cp.async into two buffers (rows padded so that fragment loads meet no bank twice).
@@ -574,7 +575,7 @@ constexpr int TC_SS = TC_KT + 4;               // row stride of the scores (floa
 
 static inline size_t tc_smem_bytes(int W) {
     const size_t ws = (size_t)W + 8;
-    return 2 * TC_KT * ws * 2 + 3 * 16 * ws * 2 + 3 * 16 * TC_PS * 2 + 16 * TC_SS * 4 + 16 * 4 * 6;
+    return 2 * TC_KT * ws * 2 + 3 * 16 * ws * 2 + 3 * 16 * TC_PS * 2 + 2 * 16 * TC_SS * 4 + 16 * 4 * 6;
 }
 
 template <int NB>                              // n-blocks of 8 columns a warp owns: C = 64 * NB
@@ -590,8 +591,8 @@ latent_scores_tc_kernel(const float* __restrict__ qk, const __nv_bfloat16* __res
     __nv_bfloat16* keys = reinterpret_cast<__nv_bfloat16*>(tc_mem);                 // [2][TC_KT][WS]
     __nv_bfloat16* qs = keys + (size_t)2 * TC_KT * WS;                              // [3][16][WS]
     __nv_bfloat16* ps = qs + (size_t)3 * 16 * WS;                                   // [3][16][TC_PS]
-    float* ss = reinterpret_cast<float*>(ps + 3 * 16 * TC_PS);                      // [16][TC_SS]
-    float* row_m = ss + 16 * TC_SS;                                                 // [16] running maximum
+    float* ss = reinterpret_cast<float*>(ps + 3 * 16 * TC_PS);                      // [2][16][TC_SS]: the scores' two halves of columns
+    float* row_m = ss + 2 * 16 * TC_SS;                                                 // [16] running maximum
     float* row_l = row_m + 16;                                                      // [16] running sum
     float* row_c = row_l + 16;                                                      // [16] this tile's correction
     int* pair_row = reinterpret_cast<int*>(row_c + 16);                             // [16] row of the pair, or -1
@@ -655,31 +656,42 @@ latent_scores_tc_kernel(const float* __restrict__ qk, const __nv_bfloat16* __res
         __syncthreads();                             // tile `it` has landed; everyone is done with the other buffer
         if (it + 1 < n_tiles) issue(t0 + TC_KT, (it + 1) & 1);
         const uint32_t kaddr = (uint32_t)__cvta_generic_to_shared(keys + (size_t)(it & 1) * TC_KT * WS);
-        // ---- scores: this warp's 8 keys
+        // ---- scores: this warp's 16 keys over its half of the columns (a query fragment serves two blocks of 8 keys)
         {
-            float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const int n0 = warp * 8;
-            for (int k0 = 0; k0 < W; k0 += 32) {
-                uint32_t b0, b1, b2, b3;         // (b0, b1): columns k0 .. k0 + 15; (b2, b3): the next sixteen
-                attn::ldmatrix_x4(kaddr + (uint32_t)((n0 + (lane & 7)) * WS + k0 + (lane >> 3) * 8) * 2, b0, b1, b2, b3);
+            float sacc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+            const int n0 = (warp & 3) * 16, half = warp >> 2;
+            const int k_begin = half * (W / 64) * 32, k_end = half == 0 ? (W / 64) * 32 : W;      // whole pairs of k-steps each
+            for (int k0 = k_begin; k0 < k_end; k0 += 32) {
                 // The instruction's own additions are cut off, not rounded, at the size of its accumulator: each 32
                 // columns start from nothing and join the score by a rounded addition, the small parts first.
-                float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float t[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
-                for (int sp = 2; sp >= 0; --sp) {
-                    uint32_t a[4];
-                    attn::ldmatrix_x4(qs_addr + (uint32_t)((sp * 16 + (lane & 15)) * WS + k0 + (lane >> 4) * 8) * 2, a[0], a[1], a[2], a[3]);
-                    attn::mma_16816(t, a, b0, b1);
-                    attn::ldmatrix_x4(qs_addr + (uint32_t)((sp * 16 + (lane & 15)) * WS + k0 + 16 + (lane >> 4) * 8) * 2, a[0], a[1], a[2], a[3]);
-                    attn::mma_16816(t, a, b2, b3);
+                for (int kk = 0; kk < 32; kk += 16) {
+                    uint32_t b0, b1, b2, b3;     // (b0, b1): keys n0 .. n0 + 7; (b2, b3): the next eight; columns k0 + kk .. + 15
+                    attn::ldmatrix_x4(kaddr + (uint32_t)((n0 + (lane & 7) + ((lane >> 4) << 3)) * WS + k0 + kk + ((lane >> 3) & 1) * 8) * 2,
+                                      b0, b1, b2, b3);
+#pragma unroll
+                    for (int sp = 2; sp >= 0; --sp) {
+                        uint32_t a[4];
+                        attn::ldmatrix_x4(qs_addr + (uint32_t)((sp * 16 + (lane & 15)) * WS + k0 + kk + (lane >> 4) * 8) * 2, a[0], a[1], a[2], a[3]);
+                        attn::mma_16816(t[0], a, b0, b1);
+                        attn::mma_16816(t[1], a, b2, b3);
+                    }
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sacc[i] += t[i];
+                for (int i = 0; i < 4; ++i) {
+                    sacc[0][i] += t[0][i];
+                    sacc[1][i] += t[1][i];
+                }
             }
-            ss[g * TC_SS + n0 + c2] = sacc[0];
-            ss[g * TC_SS + n0 + c2 + 1] = sacc[1];
-            ss[(g + 8) * TC_SS + n0 + c2] = sacc[2];
-            ss[(g + 8) * TC_SS + n0 + c2 + 1] = sacc[3];
+            float* mine = ss + half * 16 * TC_SS;
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+                mine[g * TC_SS + n0 + nb * 8 + c2] = sacc[nb][0];
+                mine[g * TC_SS + n0 + nb * 8 + c2 + 1] = sacc[nb][1];
+                mine[(g + 8) * TC_SS + n0 + nb * 8 + c2] = sacc[nb][2];
+                mine[(g + 8) * TC_SS + n0 + nb * 8 + c2 + 1] = sacc[nb][3];
+            }
         }
         __syncthreads();
         // ---- weights: pairs 2 * warp and 2 * warp + 1, two keys a lane
@@ -694,7 +706,7 @@ latent_scores_tc_kernel(const float* __restrict__ qk, const __nv_bfloat16* __res
             for (int x = 0; x < 2; ++x) {
                 const int t = t0 + lane + 32 * x;
                 valid[x] = ok && t < end && t >= plo && t <= ppos;
-                sv[x] = valid[x] ? ss[p * TC_SS + lane + 32 * x] : -INFINITY;
+                sv[x] = valid[x] ? ss[p * TC_SS + lane + 32 * x] + ss[(16 + p) * TC_SS + lane + 32 * x] : -INFINITY;
             }
             const float m_old = row_m[p];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(sv[0], sv[1])));

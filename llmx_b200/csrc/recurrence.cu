@@ -358,6 +358,7 @@ int launch_recurrence(int D, bool wide, int requests, cudaStream_t stream, const
         if (D <= 64) LLMX_WIDE(2);
         if (D <= 128) LLMX_WIDE(4);
         if (D <= 256) LLMX_WIDE(8);
+        if (D <= 512) LLMX_WIDE(16);
 #undef LLMX_WIDE
     } else {
         if (D <= 16) LLMX_REC(2, 8);
@@ -365,6 +366,7 @@ int launch_recurrence(int D, bool wide, int requests, cudaStream_t stream, const
         if (D <= 64) LLMX_REC(8, 8);
         if (D <= 128) LLMX_REC(16, 8);
         if (D <= 256) LLMX_REC(32, 8);
+        if (D <= 512) LLMX_REC(16, 32);          // a warp a column: 64 values a lane would not stay in registers
     }
 #undef LLMX_REC
     return LLMX_ERR_UNSUPPORTED;
@@ -382,7 +384,7 @@ LLMX_EXPORT int llmx_linear_recurrence(const float* q, const float* k, const flo
                                        float* out, int requests, int heads, int qk_heads, int D, int V, int max_rows,
                                        cudaStream_t stream) {
     if (requests <= 0) return 0;
-    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || D <= 0 || V <= 0 || D > 256) return LLMX_ERR_UNSUPPORTED;
+    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || D <= 0 || V <= 0 || D > 512) return LLMX_ERR_UNSUPPORTED;
     if ((decay == nullptr) == (gate == nullptr) || (gate != nullptr && beta == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
     const bool wide = max_rows > 8;            // `max_rows`: the most rows one request brings (a matter of speed only)
     if (gate)

@@ -110,7 +110,8 @@ class LatentAttention(Part):
                          slots, cache, self.kv_rank, self.rot_dim)
         q = self.uq(cq)
         o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
-        tiles = None if self.precision.invariant else step.plan_ints(self)
+        # The tiled kernels hold a cache row in a warp's registers: rows of up to 768 values.
+        tiles = None if self.precision.invariant or self.kv_rank + self.rot_dim > 768 else step.plan_ints(self)
         if tiles is not None:
             # The tiled kernels: 16 (row, head) pairs share the keys they read; key ranges fill the device when rows are few.
             host_tiles, splits = self._tiling(step.host_row_count, step.max_context)

@@ -130,6 +130,9 @@ ONE_LAYER = {
     "delta_rows_off_16_bytes": delta(heads=3, kv_heads=3, dim=8, vdim=5, conv=2),          # q/k widths of 4s in rows that are not
     "latent_18_heads": latent(heads=18, dim=8, rot_dim=4, vdim=6, q_rank=20, kv_rank=24, window=30),      # two groups of heads a tile
     "lightning_wide_heads": lightning(heads=2, dim=160, vdim=24, decay=(0.99, 0.9)),       # more than four values a lane
+    "delta_very_wide_heads": delta(heads=2, kv_heads=1, dim=320, vdim=6, conv=3, mlp=None),
+    "latent_window_of_one": latent(heads=2, dim=8, rot_dim=8, vdim=8, q_rank=16, kv_rank=16, window=1),
+    "latent_nothing_rotated": latent(heads=2, dim=8, rot_dim=4, vdim=8, q_rank=16, kv_rank=16, window=25, rot_dims=0),
 }
 
 

@@ -394,6 +394,33 @@ def test_command_line_generates_from_a_folder(tmp_path):
         seq.append(t)
 
 
+def test_command_line_logits_and_bench_take_the_folder(tmp_path):
+    make_folder(str(tmp_path), MODEL_Q, seed=16, dtype=torch.bfloat16)
+    exe = [sys.executable, os.path.join(ROOT, "bin", "llmx")]
+    logits = subprocess.run(exe + ["logits", str(tmp_path), "5,17,3,99", "--top", "3", "--dtype", "f32"], capture_output=True, text=True, timeout=600)
+    assert logits.returncode == 0 and logits.stdout.strip(), logits.stderr[-2000:]
+    bench = subprocess.run(exe + ["bench", "--model", str(tmp_path), "--p", "64", "--n", "8", "--r", "1"], capture_output=True, text=True, timeout=600)
+    assert bench.returncode == 0 and "tok" in bench.stdout, bench.stderr[-2000:]
+
+
+def test_temperature_sampling_is_reproducible_and_independent_of_the_batch(tmp_path):
+    """Four requests as mixed portions and decoded tokens, temperature 0.8 with fixed seeds: the same seeds give the same
+    replies, and a request's reply is the one it gets alone (its state and latents are its own, whatever shares the step)."""
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    cfg = MODEL_P
+    make_folder(str(tmp_path), cfg, seed=17)
+    prompts = [helpers.random_ids(cfg["vocab"], n, seed=n) for n in (1, 9, 40, 70)]
+    params = [SamplingParams(max_tokens=12, temp=0.8, top_k=40, top_p=0.95, seed=100 + i, ignore_eos=True) for i in range(4)]
+    llm = LLM(str(tmp_path), dtype="float32", kv_tokens=512, page_size=16, ubatch=32, max_seqs=4)
+    first = [o.tokens for o in llm.generate(prompts, params)]
+    again = [o.tokens for o in llm.generate(prompts, params)]
+    assert first == again
+    for i in range(4):
+        alone = LLM(str(tmp_path), dtype="float32", kv_tokens=256, page_size=16, ubatch=32, max_seqs=1).generate([prompts[i]], [params[i]])
+        assert alone[0].tokens == first[i], i
+
+
 def test_trace_run_program(tmp_path):
     cfg = MODEL_Q
     w = make_folder(str(tmp_path / "m"), cfg, seed=12, dtype=torch.bfloat16)

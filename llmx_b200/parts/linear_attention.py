@@ -9,7 +9,7 @@ For the rows of a step, per head h with key width D and value width V:
     residual += y Wo^T
 The per-head decays are constants of the architecture's configuration.  The four input projections are one product
 over the stacked weight; the activation, the recurrence (csrc/recurrence.cu) and the gated norm (csrc/rowwise.cu)
-are kernels of their own, the same for a step of one row and for a prompt's portion.
+are kernels of their own; the recurrence has a form for steps of a row or a few and one for long portions.
 """
 from __future__ import annotations
 

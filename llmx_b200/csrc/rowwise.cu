@@ -445,13 +445,24 @@ LLMX_EXPORT int llmx_scale(float* x, long long n, float s, cudaStream_t stream) 
 // ---------------------------------------------------------------------------
 constexpr int LN_MAX = 16;   // values a thread keeps (rows up to 16 * 256 wide); wider rows are read three times
 
+// `zero` (optional): a float buffer of `zero_count` values (a multiple of 4, 16-byte aligned) that the launch clears with
+// blocks of its own (those beyond `rows`): the outputs of products that follow and add their pieces with atomics.
 template <typename OutT>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
-                                 const int* __restrict__ row_index, int width, float eps) {
+                                 const int* __restrict__ row_index, int rows, int width, float eps,
+                                 float* __restrict__ zero, long long zero_count) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
+    if (r >= rows) {
+        float4* z = reinterpret_cast<float4*>(zero);
+        const long long n4 = zero_count >> 2;
+        const long long blocks = gridDim.x - rows;
+        for (long long i = (long long)(r - rows) * blockDim.x + threadIdx.x; i < n4; i += blocks * blockDim.x)
+            z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
     OutT* dst = y + (size_t)r * width;
     const float inv_n = 1.0f / (float)width;
@@ -494,17 +505,22 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 }
 
 LLMX_EXPORT int llmx_layernorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
-                               int width, float eps, cudaStream_t stream) {
+                               int width, float eps, float* zero, long long zero_count, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (width <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    if (zero && (zero_count % 4 || ((uintptr_t)zero & 15))) return LLMX_ERR_BAD_ARGUMENT;
     // The block width follows the row width alone, so a row's sums have one order whatever the batch.
     int threads = (width + LN_MAX - 1) / LN_MAX;
     threads = (threads + 31) / 32 * 32;
     threads = threads < 64 ? 64 : threads > 256 ? 256 : threads;
+    // Clearing: blocks of their own, each about four 16-byte stores a thread, at most 1,024 of them.
+    long long zero_blocks = zero ? (zero_count / 4 + 4 * threads - 1) / (4 * threads) : 0;
+    zero_blocks = zero_blocks > 1024 ? 1024 : zero_blocks;
+    const dim3 grid((unsigned)(rows + zero_blocks));
     if (out_dtype == LLMX_BF16)
-        launch_kernel(layernorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, width, eps);
+        launch_kernel(layernorm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, rows, width, eps, zero, zero_count);
     else
-        launch_kernel(layernorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)y, row_index, width, eps);
+        launch_kernel(layernorm_kernel<float>, grid, dim3(threads), 0, stream, x, w, (float*)y, row_index, rows, width, eps, zero, zero_count);
     return launch_status();
 }
 

@@ -96,7 +96,7 @@ _SIGNATURES = {
     ("rowwise", "llmx_swiglu"): [_p, _p, _i, _i, _i, _p],
     ("rowwise", "llmx_embed_scaled"): [_p, _i, _p, _p, _i, _i, _i, _f, _p],
     ("rowwise", "llmx_scale"): [_p, ctypes.c_longlong, _f, _p],
-    ("rowwise", "llmx_layernorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p],
+    ("rowwise", "llmx_layernorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p, ctypes.c_longlong, _p],
     ("rowwise", "llmx_clamped_glu"): [_p, _p, _i, _i, _i, _f, _f, _p],
     ("rowwise", "llmx_silu_columns"): [_p, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
@@ -323,9 +323,12 @@ def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-              row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = (x - mean) / sqrt(var + eps) * weight over row (row_index[i] or i); x float32, out float32 or bfloat16."""
-    _cuda(x, weight, out, row_index)
+              row_index: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = (x - mean) / sqrt(var + eps) * weight over row (row_index[i] or i); x float32, out float32 or bfloat16.
+    `zero` (optional): a float32 tensor the same launch clears (outputs of products that follow and add their pieces)."""
+    _cuda(x, weight, out, row_index, zero)
+    if zero is not None:
+        _need(zero.dtype == torch.float32 and zero.numel() % 4 == 0, "layernorm: the buffer to clear must be float32, a multiple of 4 long")
     rows, width = out.shape
     _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "layernorm: input and weight must be float32")
     _need(x.dim() == 2 and x.shape[1] == width and weight.numel() == width, "layernorm: widths do not fit")
@@ -334,7 +337,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
     else:
         _need(row_index.dtype == torch.int32 and row_index.numel() == rows, "layernorm: row_index must be int32 per row")
     _check(_fn("rowwise", "llmx_layernorm")(_ptr(x), _ptr(weight), _ptr(out), _code(out), _ptr(row_index), rows, width,
-                                            float(eps), _stream()), "layernorm")
+                                            float(eps), _ptr(zero), 0 if zero is None else zero.numel(), _stream()), "layernorm")
     return out
 
 

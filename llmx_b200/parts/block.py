@@ -95,11 +95,25 @@ class ParallelBlock(Part):
     def forward(self, x: torch.Tensor, step: StepBatch, cache_entry: Optional[int], write_cache: bool = True) -> None:
         """x: the float32 residual stream [rows, hidden], updated in place."""
         rows = x.shape[0]
-        cleared = [_cleared(p, rows, x.device, step) for p in (self.mixer, self.ffn) if p is not None]
-        h = self.norm.forward(x)
-        for z in cleared:                 # two buffers may want clearing and a norm clears one in passing: both here
+        # Products that store their result and add their pieces with atomics want their outputs cleared first: one
+        # buffer for all of the block's, cleared by the norm's launch in passing, handed back in pieces.
+        wanted = []
+        for part in (self.mixer, self.ffn):
+            for lin in (getattr(part, "stored_products", lambda: ())() if part is not None else ()):
+                n = rows * lin.out_features
+                if lin.adds_pieces(rows) and n % 4 == 0:
+                    wanted.append((part, lin, n))
+        flat = torch.empty(sum(n for _, _, n in wanted), dtype=torch.float32, device=x.device) if wanted else None
+        # Parts with the older way of asking (`wants_cleared`) get theirs cleared by a call of its own.
+        others = [_cleared(p, rows, x.device, step) for p in (self.mixer, self.ffn) if p is not None and not hasattr(p, "stored_products")]
+        h = self.norm.forward(x, zero=flat)
+        for z in others:
             if z is not None:
                 z.zero_()
+        at = 0
+        for part, lin, n in wanted:
+            part.cleared_outputs[id(lin)] = flat[at:at + n].view(rows, lin.out_features)
+            at += n
         self.mixer.forward(h, step, cache_entry, x, write_cache)
         if self.ffn is not None:
             self.ffn.forward(h, step, x)

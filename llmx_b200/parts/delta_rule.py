@@ -23,7 +23,7 @@ from .. import ops, runtime
 from ..cache.manager import StateSpec
 from ..weights.spec import TensorSpec
 from .base import Part, Precision, StepBatch
-from .linear import Linear
+from .linear import Linear, stored_product
 
 
 class GatedDeltaRule(Part):
@@ -38,6 +38,10 @@ class GatedDeltaRule(Part):
         self.channels = 2 * self.qk_width + self.v_width
         self.state_floats = self.heads * self.value_dim * self.key_dim
         self.slot_floats = self.state_floats + (self.taps - 1) * self.channels
+
+    def stored_products(self):
+        """The products whose result is stored (not added to the residual): a block may clear their outputs in passing."""
+        return (self.inputs,)
 
     def cache_spec(self):
         return StateSpec((self.slot_floats,), "float32")
@@ -54,6 +58,7 @@ class GatedDeltaRule(Part):
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
+        self.cleared_outputs = {}
         t = tensors
         self.inputs = Linear(torch.cat([t["q"], t["k"], t["v"], t["g"], t["b"], t["a"]], dim=0), precision)
         self.o = Linear(t["o"], precision)
@@ -71,7 +76,7 @@ class GatedDeltaRule(Part):
         qk, vw, H = self.qk_width, self.v_width, self.heads
         g_off = self.channels
         b_off, a_off = g_off + vw, g_off + vw + H
-        proj = self.inputs(h)                                             # [rows, q | k | v | g | b | a]
+        proj = stored_product(self, self.inputs, h)                                             # [rows, q | k | v | g | b | a]
         state = step.state(cache_entry)
         ready = torch.empty((rows, self.channels), dtype=torch.float32, device=h.device)
         gates = torch.empty((rows, 2 * H), dtype=torch.float32, device=h.device)

@@ -95,8 +95,10 @@ class LogitsHead(Part):
         return self._native.handle if self._native is not None else None
 
     def forward(self, x: torch.Tensor, logit_rows: torch.Tensor) -> torch.Tensor:
-        h = self.norm.forward(x, row_index=logit_rows)
-        logits = self.linear(h)
+        rows = logit_rows.numel()
+        out = self.linear.output_to_clear(rows, x.device)          # cleared by the norm's launch when the product adds pieces
+        h = self.norm.forward(x, row_index=logit_rows, zero=out)
+        logits = self.linear(h, out=out, cleared=True) if out is not None else self.linear(h)
         if self.scale != 1.0:
             from .. import ops
             ops.scale_(logits, self.scale)

@@ -23,7 +23,7 @@ from .. import ops, runtime
 from ..cache.manager import KVSpec
 from ..weights.spec import TensorSpec
 from .base import Part, PartPlan, Precision, StepBatch, StepShape
-from .linear import Linear
+from .linear import Linear, stored_product
 
 
 class _TilePlan(PartPlan):
@@ -52,6 +52,10 @@ class LatentAttention(Part):
         self.freq: Optional[torch.Tensor] = None
         self.plain_cores = False      # True: the tiled scores stay on the CUDA cores also where the tensor-core form would run
 
+    def stored_products(self):
+        """The products whose result is stored (not added to the residual): a block may clear their outputs in passing."""
+        return (self.down, self.uq)
+
     def cache_spec(self):
         return KVSpec(1, self.kv_rank + self.rot_dim, self.window, planes=1)
 
@@ -65,6 +69,7 @@ class LatentAttention(Part):
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
+        self.cleared_outputs = {}
         t = tensors
         self.down = Linear(torch.cat([t["dq"], t["dkv"]], dim=0), precision)      # one product for both latents
         self.uq, self.o = Linear(t["uq"], precision), Linear(t["o"], precision)
@@ -106,9 +111,9 @@ class LatentAttention(Part):
         group, cache = step.kv(cache_entry)
         cq = torch.empty((rows, self.q_rank), dtype=self.precision.act, device=h.device)
         slots = group.slots if write_cache else torch.full((rows,), -1, dtype=torch.int32, device=h.device)
-        ops.latent_write(self.down(h), self.q_rank, self.dq_norm, cq, self.dkv_norm, self.norm_eps, self.freq, step.positions,
+        ops.latent_write(stored_product(self, self.down, h), self.q_rank, self.dq_norm, cq, self.dkv_norm, self.norm_eps, self.freq, step.positions,
                          slots, cache, self.kv_rank, self.rot_dim)
-        q = self.uq(cq)
+        q = stored_product(self, self.uq, cq)
         o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
         # The tiled kernels hold a cache row in a warp's registers: rows of up to 768 values.
         tiles = None if self.precision.invariant or self.kv_rank + self.rot_dim > 768 else step.plan_ints(self)

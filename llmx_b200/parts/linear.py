@@ -44,6 +44,14 @@ def call_struct(step, part, device, workspace_of):
     return probe, ws
 
 
+def stored_product(part, lin: "Linear", a: torch.Tensor) -> torch.Tensor:
+    """`lin(a)` into the output the block had cleared for it (see ParallelBlock), or into a fresh one."""
+    out = part.cleared_outputs.pop(id(lin), None) if hasattr(part, "cleared_outputs") else None
+    if out is not None and out.shape[0] == a.shape[0]:
+        return lin(a, out=out, cleared=True)
+    return lin(a)
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, precision: Precision):
         # A weight stored in 32-bit is rounded once for the bfloat16 path; a bfloat16 weight

@@ -21,7 +21,7 @@ from .. import ops, runtime
 from ..cache.manager import StateSpec
 from ..weights.spec import TensorSpec
 from .base import Part, Precision, StepBatch
-from .linear import Linear
+from .linear import Linear, stored_product
 
 
 class DecayedLinearAttention(Part):
@@ -33,6 +33,10 @@ class DecayedLinearAttention(Part):
         self.decay_values = [float(d) for d in decay]
         self.norm_eps, self.names = float(norm_eps), tuple(names)
         self.qk_width, self.v_width = self.heads * self.key_dim, self.heads * self.value_dim
+
+    def stored_products(self):
+        """The products whose result is stored (not added to the residual): a block may clear their outputs in passing."""
+        return (self.inputs,)
 
     def cache_spec(self):
         return StateSpec((self.heads * self.value_dim * self.key_dim,), "float32")
@@ -46,6 +50,7 @@ class DecayedLinearAttention(Part):
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
+        self.cleared_outputs = {}
         q, k, v, g, o, norm = self.names
         self.inputs = Linear(torch.cat([tensors[q], tensors[k], tensors[v], tensors[g]], dim=0), precision)
         self.o = Linear(tensors[o], precision)
@@ -59,7 +64,7 @@ class DecayedLinearAttention(Part):
                 and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
             raise runtime.KernelError("linear attention: rows of the path's type and the mixer's width, a float32 residual")
         qk, vw = self.qk_width, self.v_width
-        proj = self.inputs(h)                                             # [rows, q | k | v | g]
+        proj = stored_product(self, self.inputs, h)                                             # [rows, q | k | v | g]
         ops.silu_columns_(proj, 0, 2 * qk + vw)
         o = torch.empty((rows, vw), dtype=torch.float32, device=h.device)
         ops.linear_recurrence(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vw], step.state(cache_entry), step, o,

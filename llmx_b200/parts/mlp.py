@@ -14,7 +14,7 @@ import torch
 from .. import runtime
 from ..weights.spec import TensorSpec
 from .base import NativeHandle, Part, Precision, StepBatch
-from .linear import Linear, call_struct
+from .linear import Linear, call_struct, stored_product
 
 
 class GatedMLP(Part):
@@ -81,8 +81,12 @@ class ClampedGLU(Part):
         return {g: TensorSpec((self.intermediate, self.hidden)), u: TensorSpec((self.intermediate, self.hidden)),
                 d: TensorSpec((self.hidden, self.intermediate))}
 
+    def stored_products(self):
+        return (self.gate_up,)
+
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
+        self.cleared_outputs = {}
         g, u, d = self.names
         self.gate_up = Linear(torch.cat([tensors[g], tensors[u]], dim=0), precision)
         self.down = Linear(tensors[d], precision)
@@ -93,7 +97,7 @@ class ClampedGLU(Part):
         if not (h.is_cuda and h.is_contiguous() and h.dtype is self.precision.act and tuple(h.shape) == (rows, self.hidden)
                 and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
             raise runtime.KernelError("feed-forward: rows of the path's type and the part's width, a float32 residual")
-        gu = self.gate_up(h)
+        gu = stored_product(self, self.gate_up, h)
         act = torch.empty((rows, self.intermediate), dtype=self.precision.act, device=h.device)
         ops.clamped_glu(gu, act, self.limit, self.alpha)
         self.down(act, out=residual, accumulate=True)

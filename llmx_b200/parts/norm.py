@@ -79,9 +79,10 @@ class LayerNorm(Part):
                 row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                 zero: Optional[torch.Tensor] = None) -> torch.Tensor:
         from .. import ops
-        if zero is not None:
-            zero.zero_()
         rows = x.shape[0] if row_index is None else row_index.numel()
         if out is None:
             out = torch.empty((rows, self.width), dtype=out_dtype or self.precision.act, device=x.device)
-        return ops.layernorm(x, self.weight, self.eps, out, row_index)
+        if zero is not None and (zero.numel() % 4 or zero.data_ptr() % 16):
+            zero.zero_()
+            zero = None
+        return ops.layernorm(x, self.weight, self.eps, out, row_index, zero)

@@ -158,6 +158,14 @@ def test_row_kernels_against_the_plain_functions():
         out = torch.empty(3, width, dtype=torch.float32, device=DEV)
         ops.layernorm(x.to(DEV), wt.to(DEV), 1e-5, out, row_index=idx.to(DEV))
         assert np.abs(out.cpu().numpy() - plain.layer_norm(x.numpy()[[4, 0, 4]], wt.numpy(), 1e-5)).max() <= 1e-5
+    # A buffer handed to the norm's launch is cleared by it, whatever its size against the rows'.
+    for count in (4, 1000, 1 << 20):
+        junk = torch.full((count,), 7.0, dtype=torch.float32, device=DEV)
+        x = torch.randn(3, 96, generator=g)
+        out = torch.empty(3, 96, dtype=torch.float32, device=DEV)
+        ops.layernorm(x.to(DEV), torch.ones(96, device=DEV), 1e-5, out, zero=junk)
+        assert float(junk.abs().max()) == 0.0
+        assert np.abs(out.cpu().numpy() - plain.layer_norm(x.numpy(), np.ones(96), 1e-5)).max() <= 1e-5
     # The clamped gated unit: values on both sides of the limit on both branches.
     gu = torch.randn(6, 2 * 37, generator=g) * 3
     out = torch.empty(6, 37, dtype=torch.float32, device=DEV)

@@ -37,6 +37,7 @@ class KVSpec:
     head_dim: int
     window: Optional[int] = None      # None: every key is kept
     planes: int = 2                   # 2: keys and values; 1: one vector per token (a latent that keys and values are made from)
+    chunk: Optional[int] = None       # a position sees only the keys of its own chunk of this many positions (counted from 0)
 
 
 @dataclass(frozen=True)
@@ -106,7 +107,7 @@ class RequestCache:
     def __init__(self, manager: "CacheManager", request_id: Hashable):
         self.manager = manager
         self.request_id = request_id
-        self.tables: List[BlockTable] = [BlockTable(g.pool, g.page_size, g.spec.window) for g in manager.groups]
+        self.tables: List[BlockTable] = [BlockTable(g.pool, g.page_size, g.spec.window, g.spec.chunk) for g in manager.groups]
         self.state_slot: int = -1          # where the request's state lies (read by a step)
         self.state_slot_out: int = -1      # where a step writes the state it leaves; the two swap at commit
         if manager.has_state:
@@ -162,7 +163,7 @@ class RequestCache:
         if self.state_slot >= 0:
             raise RuntimeError("a request whose layers keep fixed-size state cannot be rolled back")
         for t in self.tables:
-            if t.window is not None and length < t._first_live * t.page_size:
+            if (t.window is not None or t.chunk is not None) and length < t._first_live * t.page_size:
                 raise RuntimeError("KV cache: cannot roll back into pages the window has given back")
         for t in self.tables:
             t.truncate(length)
@@ -209,7 +210,7 @@ class CacheManager:
             if isinstance(s, KVSpec):
                 by_spec.setdefault(s, []).append(i)
         self.groups: List[CacheGroup] = [
-            CacheGroup(s, m, self.page_size, (self.kv_tokens if s.window is None else self.window_kv_tokens) // self.page_size)
+            CacheGroup(s, m, self.page_size, (self.kv_tokens if s.window is None and s.chunk is None else self.window_kv_tokens) // self.page_size)
             for s, m in by_spec.items()]
         self.group_of_entry: Dict[int, Tuple[int, int]] = {}
         for gi, g in enumerate(self.groups):
@@ -272,10 +273,11 @@ class CacheManager:
         """
         out = []
         for g in self.groups:
-            if g.spec.window is None:
+            spans = [x for x in (g.spec.window, g.spec.chunk) if x is not None]
+            if not spans:
                 held = tokens
             else:
-                held = min(tokens, g.spec.window + g.page_size + max(step_tokens, 1) + g.page_size)
+                held = min(tokens, min(spans) + g.page_size + max(step_tokens, 1) + g.page_size)
             out.append(-(-held // g.page_size))
         return out
 

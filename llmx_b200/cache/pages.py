@@ -78,17 +78,23 @@ class BlockTable:
     `window`: None keeps every key; W keeps, for a query at position p, the
     keys p-W+1..p, so once `length` tokens are committed no later query needs a
     key below length-W+1 and the pages wholly below that are given back (their
-    entries become RELEASED and are never read again).
+    entries become RELEASED and are never read again).  `chunk`: C lets a
+    query at position p see only the keys from floor(p / C) * C on, so once
+    `length` tokens are committed the pages wholly below the chunk of position
+    `length` are given back the same way.
     """
 
-    def __init__(self, pool: PagePool, page_size: int, window: Optional[int] = None):
+    def __init__(self, pool: PagePool, page_size: int, window: Optional[int] = None, chunk: Optional[int] = None):
         if page_size <= 0:
             raise ValueError("a page holds at least one token")
         if window is not None and window <= 0:
             raise ValueError("a window holds at least one key")
         self.pool = pool
         self.page_size = int(page_size)
+        if chunk is not None and chunk <= 0:
+            raise ValueError("a chunk holds at least one position")
         self.window = window
+        self.chunk = chunk
         self.pages: List[int] = []
         self.length = 0          # committed tokens
         self.pending = 0         # prepared, not yet committed
@@ -136,9 +142,11 @@ class BlockTable:
         self._taken_by_prepare = 0
 
     def _release_passed(self) -> None:
-        if self.window is None:
+        if self.window is None and self.chunk is None:
             return
-        lowest_needed = self.length - self.window + 1
+        lowest_needed = 0 if self.window is None else self.length - self.window + 1
+        if self.chunk is not None:
+            lowest_needed = max(lowest_needed, (self.length // self.chunk) * self.chunk)
         if lowest_needed <= 0:
             return
         upto = min(lowest_needed // self.page_size, len(self.pages))

@@ -2,5 +2,6 @@
 from .base import ConfigError, ModelConfig, Rule, apply_rules, read_config_json
 from .qwen3 import Qwen3Config, YarnScaling
 from .buzetar import BuzetarConfig
+from .kisepel import KisepelConfig
 
-__all__ = ["ConfigError", "ModelConfig", "Rule", "apply_rules", "read_config_json", "Qwen3Config", "YarnScaling", "BuzetarConfig"]
+__all__ = ["ConfigError", "ModelConfig", "Rule", "apply_rules", "read_config_json", "Qwen3Config", "YarnScaling", "BuzetarConfig", "KisepelConfig"]

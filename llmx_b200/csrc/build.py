@@ -44,7 +44,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
-    "recurrence": ["recurrence.cu"],          # matrix-state recurrences (decayed linear attention, gated delta rule) and the short convolution
+    "recurrence": ["recurrence.cu"],          # matrix-state recurrences (decayed linear attention, gated delta rule, selective state space) and the short convolution
+    "attention_split": ["attention_split.cu"],     # softmax attention with key and value widths of their own, windows and chunks
+    "moe": ["moe.cu"],                        # experts chosen by a table: routing on the device, grouped products
     "latent_attention": ["latent_attention.cu"],   # attention over a cache of latents
     "selftest": ["selftest.cu"],              # the bounded wait made to run out on purpose (tests)
     "runtime": ["runtime/runtime.cpp", "runtime/engine.cpp", "runtime/loader.cpp"],       # host code: the parts' forward passes (no kernels of its own)

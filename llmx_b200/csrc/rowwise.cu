@@ -584,7 +584,7 @@ LLMX_EXPORT int llmx_silu_columns(float* x, int rows, int stride, int c0, int n,
 template <typename OutT>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride,
                                      const float* __restrict__ w, int w_len, OutT* __restrict__ y, int groups, int group,
-                                     float eps, int gate_kind) {
+                                     float eps, int gate_kind, int gate_first) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
@@ -592,19 +592,26 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
     const size_t base = ((size_t)r * groups + j) * group;
     const float* src = o + base;
     const float* gsrc = gate + (size_t)r * gate_stride + (size_t)j * group;
+    auto act = [&](float g) {
+        const float sg = 1.0f / (1.0f + expf(-g));
+        return gate_kind == 0 ? sg : g * sg;
+    };
     float s = 0.0f;
-    for (int i = threadIdx.x; i < group; i += blockDim.x) s = fmaf(src[i], src[i], s);
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const float x = gate_first ? src[i] * act(gsrc[i]) : src[i];
+        s = fmaf(x, x, s);
+    }
     const float rr = 1.0f / sqrtf(block_sum(s, scratch) / (float)group + eps);
     for (int i = threadIdx.x; i < group; i += blockDim.x) {
-        const float g = gsrc[i];
-        const float sg = 1.0f / (1.0f + expf(-g));
-        const float a = gate_kind == 0 ? sg : g * sg;
-        y[base + i] = from_float<OutT>(src[i] * rr * w[(j * group + i) % w_len] * a);
+        const float a = act(gsrc[i]);
+        const float wi = w[(j * group + i) % w_len];
+        y[base + i] = from_float<OutT>(gate_first ? (src[i] * a) * rr * wi : src[i] * rr * wi * a);
     }
 }
 
+// `gate_first` 0: y = o / rms(o) * w * act(gate).  1: the gate comes before the norm: z = o * act(gate), y = z / rms(z) * w.
 LLMX_EXPORT int llmx_gated_rmsnorm(const float* o, const float* gate, int gate_stride, const float* w, int w_len, void* y,
-                                   int out_dtype, int rows, int groups, int group, float eps, int gate_kind,
+                                   int out_dtype, int rows, int groups, int group, float eps, int gate_kind, int gate_first,
                                    cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (groups <= 0 || group <= 0 || w_len <= 0 || groups > 65535 || (gate_kind != 0 && gate_kind != 1)) return LLMX_ERR_BAD_ARGUMENT;
@@ -612,8 +619,52 @@ LLMX_EXPORT int llmx_gated_rmsnorm(const float* o, const float* gate, int gate_s
     threads = (threads + 31) / 32 * 32;
     threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
     if (out_dtype == LLMX_BF16)
-        launch_kernel(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (__nv_bfloat16*)y, groups, group, eps, gate_kind);
+        launch_kernel(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (__nv_bfloat16*)y, groups, group, eps, gate_kind, gate_first);
     else
-        launch_kernel(gated_rmsnorm_kernel<float>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (float*)y, groups, group, eps, gate_kind);
+        launch_kernel(gated_rmsnorm_kernel<float>, dim3(rows, groups), dim3(threads), 0, stream, o, gate, gate_stride, w, w_len, (float*)y, groups, group, eps, gate_kind, gate_first);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Two mixers side by side: x[r] += factor * (a[r] / rms(a[r]) * wa + b[r] / rms(b[r]) * wb), each side normed over
+// the whole row with a plain weight of its own.  One block a row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+pair_norm_add_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa,
+                     const float* __restrict__ wb, float* __restrict__ x, int width, float eps, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        sa = fmaf(a[base + i], a[base + i], sa);
+        sb = fmaf(b[base + i], b[base + i], sb);
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, scratch) / (float)width + eps);
+    const float rb = 1.0f / sqrtf(block_sum(sb, scratch) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        x[base + i] += factor * (a[base + i] * ra * wa[i] + b[base + i] * rb * wb[i]);
+}
+
+LLMX_EXPORT int llmx_pair_norm_add(const float* a, const float* b, const float* wa, const float* wb, float* x, int rows,
+                                   int width, float eps, float factor, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    launch_kernel(pair_norm_add_kernel, dim3(rows), dim3(256), 0, stream, a, b, wa, wb, x, width, eps, factor);
+    return launch_status();
+}
+
+// x[i] += y[i] over flat float buffers (a model that adds its embedding output to the stream again).
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += y[i];
+}
+
+LLMX_EXPORT int llmx_add(float* x, const float* y, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    launch_kernel(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, y, n);
     return launch_status();
 }

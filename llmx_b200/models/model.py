@@ -5,7 +5,11 @@ It may name a block twice (the same weights run again, on a cache entry of
 their own or on a shared one) and may let a block read the cache entry another
 block wrote (`write_cache=False`).  Cache entries are numbered by the model;
 what each needs (`KVSpec`, `StateSpec` or nothing) is asked of the mixer of the
-first step that names it.
+first step that names it.  A mixer made of several (two side by side) needs
+several entries: its `cache_spec()` is a tuple, and the step names as many entries.
+A step may also ask for the embedding output (the stream as it was before the
+first layer) to be added to the stream before its block runs (`add_embedding`),
+for a model that runs a stretch of layers several times.
 
 `Model` knows no architecture.  An architecture's builder
 (`llmx_b200/models/qwen3.py`) constructs the parts from its configuration and
@@ -15,7 +19,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 import ctypes
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Set, Tuple, Union
 
 import numpy as np
 import torch
@@ -30,8 +34,14 @@ from ..weights.spec import TensorSpec
 @dataclass(frozen=True)
 class LayerStep:
     block: int                          # index into Model.blocks
-    cache_entry: Optional[int] = None   # index of the cache entry the mixer uses (None: the mixer has no cache)
+    cache_entry: Optional[Union[int, Tuple[int, ...]]] = None   # index of the cache entry the mixer uses (None: the mixer has
+    #                                     no cache; a tuple: one entry for each spec of a mixer that needs several)
     write_cache: bool = True            # False: read the entry another step wrote
+    add_embedding: bool = False         # the embedding output is added to the stream before the block runs
+
+
+def _as_tuple(x) -> tuple:
+    return () if x is None else tuple(x) if isinstance(x, (tuple, list)) else (x,)
 
 
 class ModelPlan:
@@ -99,23 +109,27 @@ class Model:
 
     def _check_order(self) -> None:
         writers: Dict[int, int] = {}
+        named = set()
         for n, s in enumerate(self.order):
             if not 0 <= s.block < len(self.blocks):
                 raise ValueError(f"layer order step {n} names block {s.block}, the model has {len(self.blocks)}")
-            spec = self.blocks[s.block].cache_spec()
-            if spec is None:
-                if s.cache_entry is not None:
+            specs, entries = _as_tuple(self.blocks[s.block].cache_spec()), _as_tuple(s.cache_entry)
+            if not specs:
+                if entries:
                     raise ValueError(f"layer order step {n}: block {s.block} has no cache but an entry is named")
                 continue
-            if s.cache_entry is None:
-                raise ValueError(f"layer order step {n}: block {s.block} needs a cache entry")
-            if s.write_cache:
-                if s.cache_entry in writers:
-                    raise ValueError(f"layer order steps {writers[s.cache_entry]} and {n} both write cache entry {s.cache_entry}")
-                writers[s.cache_entry] = n
-            elif s.cache_entry not in writers:
-                raise ValueError(f"layer order step {n} reads cache entry {s.cache_entry} before any step wrote it")
-        entries = sorted({s.cache_entry for s in self.order if s.cache_entry is not None})
+            if len(entries) != len(specs):
+                raise ValueError(f"layer order step {n}: block {s.block} needs {len(specs)} cache "
+                                 f"{'entry' if len(specs) == 1 else 'entries'}" + (f", {len(entries)} named" if entries else ""))
+            for e in entries:
+                named.add(e)
+                if s.write_cache:
+                    if e in writers:
+                        raise ValueError(f"layer order steps {writers[e]} and {n} both write cache entry {e}")
+                    writers[e] = n
+                elif e not in writers:
+                    raise ValueError(f"layer order step {n} reads cache entry {e} before any step wrote it")
+        entries = sorted(named)
         if entries != list(range(len(entries))):
             raise ValueError("cache entries must be numbered 0..n-1 without gaps")
 
@@ -123,12 +137,10 @@ class Model:
     def cache_entry_specs(self) -> list:
         specs: Dict[int, object] = {}
         for s in self.order:
-            if s.cache_entry is None:
-                continue
-            spec = self.blocks[s.block].cache_spec()
-            if s.cache_entry in specs and specs[s.cache_entry] != spec:
-                raise ValueError(f"cache entry {s.cache_entry} is used by mixers with different needs")
-            specs[s.cache_entry] = spec
+            for e, spec in zip(_as_tuple(s.cache_entry), _as_tuple(self.blocks[s.block].cache_spec())):
+                if e in specs and specs[e] != spec:
+                    raise ValueError(f"cache entry {e} is used by mixers with different needs")
+                specs[e] = spec
         return [specs[i] for i in range(len(specs))]
 
     # -- tensors -----------------------------------------------------------------
@@ -192,7 +204,8 @@ class Model:
             self._native_tried = True
             blocks = [b.native for b in self.blocks]
             emb, head = self.embedding.native, self.head.native
-            if emb and head and all(blocks):
+            plain = all(not s.add_embedding and not isinstance(s.cache_entry, (tuple, list)) for s in self.order)
+            if emb and head and all(blocks) and plain:
                 arr = (ctypes.c_void_p * len(blocks))(*blocks)
                 order = (runtime.LayerStepStruct * len(self.order))(*[
                     runtime.LayerStepStruct(s.block, -1 if s.cache_entry is None else s.cache_entry, 1 if s.write_cache else 0)
@@ -242,7 +255,13 @@ class Model:
             runtime.check(rt.llmx_model_forward(self.native, ctypes.byref(s), runtime.ptr(logits)), "forward")
             return logits
         x = self.embedding.forward(step.token_ids)
+        x0 = None
+        if any(s.add_embedding for s in self.order):
+            x0 = x.clone()
         for s in self.order:
+            if s.add_embedding:
+                from .. import ops
+                ops.add_(x, x0)
             self.blocks[s.block].forward(x, step, s.cache_entry, s.write_cache)
         if wanted == 0:
             return None

@@ -99,11 +99,18 @@ _SIGNATURES = {
     ("rowwise", "llmx_layernorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p, ctypes.c_longlong, _p],
     ("rowwise", "llmx_clamped_glu"): [_p, _p, _i, _i, _i, _f, _f, _p],
     ("rowwise", "llmx_silu_columns"): [_p, _i, _i, _i, _i, _p],
-    ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
-    ("recurrence", "llmx_linear_recurrence"): [_p, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, ctypes.c_longlong, _p, _p, _p, _p,
-                                               _p, _p, _i, _i, _i, _i, _i, _i, _p],
-    ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p,
-                                          ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
+    ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _i, _p],
+    ("rowwise", "llmx_pair_norm_add"): [_p, _p, _p, _p, _p, _i, _i, _f, _f, _p],
+    ("rowwise", "llmx_add"): [_p, _p, ctypes.c_longlong, _p],
+    ("recurrence", "llmx_linear_recurrence"): [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _i, _p, _p, ctypes.c_longlong, _p, _p,
+                                               _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _i, _i, _f,
+                                          _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
+    ("attention_split", "llmx_qk_norm_rope_write"): [_p, _i, _p, _p, _f, _p, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+    ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    ("moe", "llmx_moe_route"): [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p],
+    ("moe", "llmx_moe_product"): [_p, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _p],
+    ("moe", "llmx_moe_combine"): [_p, _p, _i, _i, _i, _f, _p],
     ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
@@ -360,8 +367,9 @@ def silu_columns_(x: torch.Tensor, first: int, count: int) -> torch.Tensor:
 
 
 def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group: int, gate_kind: str,
-                  out: torch.Tensor) -> torch.Tensor:
+                  out: torch.Tensor, gate_first: bool = False) -> torch.Tensor:
     """out = o / sqrt(mean over each group of `group` values of o^2 + eps) * weight * act(gate); act sigmoid or silu.
+    `gate_first`: the gate comes before the norm: z = o * act(gate), out = z / sqrt(mean z^2 + eps) * weight.
     o float32 [rows, width] contiguous; gate float32 [rows, width], a view whose rows may be strided; weight float32 of
     the row's width, or of one group's width and shared by the groups."""
     _need(o.is_cuda and gate.is_cuda and weight.is_cuda and out.is_cuda, "kernel arguments must be CUDA tensors (there is no CPU path)")
@@ -373,8 +381,30 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     _need(gate_kind in ("sigmoid", "silu"), "gated_rmsnorm: gate must be sigmoid or silu")
     _check(_fn("rowwise", "llmx_gated_rmsnorm")(_ptr(o), _ptr(gate), gate.stride(0) if rows > 1 else width, _ptr(weight),
                                                 weight.numel(), _ptr(out), _code(out), rows, width // group, group,
-                                                float(eps), 0 if gate_kind == "sigmoid" else 1, _stream()), "gated_rmsnorm")
+                                                float(eps), 0 if gate_kind == "sigmoid" else 1, 1 if gate_first else 0, _stream()),
+           "gated_rmsnorm")
     return out
+
+
+def pair_norm_add_(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+                   factor: float) -> torch.Tensor:
+    """x += factor * (a / rms(a) * wa + b / rms(b) * wb), each row of a and b normed over its whole width; all float32."""
+    _cuda(x, a, b, wa, wb)
+    rows, width = x.shape
+    _need(all(t.dtype == torch.float32 for t in (x, a, b, wa, wb)), "pair_norm_add: float32 tensors")
+    _need(tuple(a.shape) == (rows, width) and tuple(b.shape) == (rows, width) and wa.numel() == width and wb.numel() == width,
+          "pair_norm_add: shapes do not fit")
+    _check(_fn("rowwise", "llmx_pair_norm_add")(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(x), rows, width, float(eps),
+                                                float(factor), _stream()), "pair_norm_add")
+    return x
+
+
+def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x += y; float32 tensors of one shape."""
+    _cuda(x, y)
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and x.shape == y.shape, "add: float32 tensors of one shape")
+    _check(_fn("rowwise", "llmx_add")(_ptr(x), _ptr(y), x.numel(), _stream()), "add")
+    return x
 
 
 # ---------------------------------------------------------------------------
@@ -386,57 +416,176 @@ def _strided_rows(t: torch.Tensor, what: str) -> int:
 
 def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
                       heads: int, qk_heads: int, key_dim: int, value_dim: int, decay: Optional[torch.Tensor] = None,
-                      gate: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None, form: Optional[str] = None,
+                      skip: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per (request, head): S <- a S + k u^T, o = S^T q over the step's rows in order, S [D, V] float32 carried in the
-    request's state slot.  With `decay` [heads]: a = decay_h, u = v.  With `gate`, `beta` [rows, heads] (views):
-    a = gate, u = beta (v - a S^T k), the gated delta rule.  q, k [rows, qk_heads * D], v [rows, heads * V]: float32
-    views whose rows may be strided.  state [slots, floats]: the recurrence's values first, [H][V][D].
-    `step`: the StepBatch (row ranges, histories and slots are read on the device)."""
+    request's state slot.  `form` (default: "decay" with `decay`, else "delta"):
+      "decay"          a = decay_h [heads], u = v
+      "delta"          a = gate, u = beta (v - a S^T k); gate, beta [rows, heads] (views)
+      "scaled"         a = gate, u = beta v, o += skip_h v; gate, beta [rows, heads], skip [heads] or None
+      "delta_channel"  S <- diag(gate) S first, gate [rows, heads * D]; then u = beta (v - S^T k), S <- S + k u^T
+    q, k [rows, qk_heads * D], v [rows, heads * V]: float32 views whose rows may be strided.  state [slots, floats]: the
+    recurrence's values first, [H][V][D].  `step`: the StepBatch (row ranges, histories and slots are read on the device)."""
     rows = q.shape[0]
     qs, ks, vs = _strided_rows(q, "recurrence q"), _strided_rows(k, "recurrence k"), _strided_rows(v, "recurrence v")
     _need(q.shape[1] == qk_heads * key_dim and k.shape[1] == qk_heads * key_dim and v.shape[1] == heads * value_dim
           and k.shape[0] == rows and v.shape[0] == rows, "recurrence: q, k, v shapes do not fit")
-    _cuda(state, out, decay)
+    _cuda(state, out, decay, skip)
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] >= heads * key_dim * value_dim, "recurrence: state slots too small")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (rows, heads * value_dim), "recurrence: output shape does not fit")
-    gs = 0
-    if gate is not None:
-        _need(beta is not None and decay is None, "recurrence: the delta rule takes gate and beta and no constant decay")
-        gs = _strided_rows(gate, "recurrence gate")
-        _need(_strided_rows(beta, "recurrence beta") == gs and tuple(gate.shape) == (rows, heads) and tuple(beta.shape) == (rows, heads),
-              "recurrence: gate and beta must be views of one matrix, [rows, heads]")
+    if form is None:
+        form = "delta" if gate is not None else "decay"
+    _need(form in ("decay", "delta", "scaled", "delta_channel"), "recurrence: unknown form")
+    mode = ("decay", "delta", "scaled", "delta_channel").index(form)
+    gs = bs = 0
+    if mode == 0:
+        _need(decay is not None and decay.dtype == torch.float32 and decay.numel() == heads and gate is None, "recurrence: decay float32 [heads]")
     else:
-        _need(decay is not None and decay.dtype == torch.float32 and decay.numel() == heads, "recurrence: decay float32 [heads]")
+        _need(gate is not None and beta is not None and decay is None, "recurrence: this form takes gate and beta and no constant decay")
+        gs, bs = _strided_rows(gate, "recurrence gate"), _strided_rows(beta, "recurrence beta")
+        _need(tuple(gate.shape) == (rows, heads * key_dim if mode == 3 else heads) and tuple(beta.shape) == (rows, heads),
+              "recurrence: gate [rows, heads] (or [rows, heads * D] per key channel) and beta [rows, heads]")
+    if skip is not None:
+        _need(mode == 2 and skip.dtype == torch.float32 and skip.numel() == heads, "recurrence: skip float32 [heads], scaled form only")
     _check(_fn("recurrence", "llmx_linear_recurrence")(
-        _ptr(q), _ptr(k), _ptr(v), qs, ks, vs, _ptr(decay), _ptr(gate), _ptr(beta), gs, _ptr(state), state.shape[1],
-        _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out),
-        _ptr(out), step.requests, heads, qk_heads, key_dim, value_dim, int(step.max_row_count), _stream()), "linear_recurrence")
+        _ptr(q), _ptr(k), _ptr(v), qs, ks, vs, mode, _ptr(decay), _ptr(gate), _ptr(beta), gs, bs, _ptr(skip), _ptr(state),
+        state.shape[1], _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots),
+        _ptr(step.state_slots_out), _ptr(out), step.requests, heads, qk_heads, key_dim, value_dim, int(step.max_row_count),
+        _stream()), "linear_recurrence")
     return out
 
 
 def conv_prepare(proj: torch.Tensor, channels: int, q_channels: int, k_channels: int, taps_w: torch.Tensor,
                  ready: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, b_off: int, a_off: int,
                  gates: torch.Tensor, heads: int, key_dim: int, q_factor: float, state: torch.Tensor, conv_off: int,
-                 step) -> None:
-    """The short causal convolution, silu, unit q/k heads and the gates of a delta-rule mixer (csrc/recurrence.cu).
-    The request's slot read and the slot written must differ (a step reads one and writes its spare)."""
-    _cuda(proj, taps_w, ready, a_log, dt_bias, gates, state)
+                 step, first: int = 0, bias: Optional[torch.Tensor] = None, gate_kind: str = "delta",
+                 decay_in: Optional[torch.Tensor] = None) -> None:
+    """The short causal convolution (+ `bias`), silu, unit q/k heads and the gates of a recurrent mixer
+    (csrc/recurrence.cu).  The filtered channels are columns first .. first + channels - 1 of `proj`.  `gate_kind`:
+    "delta": gates [rows, 2 heads] = g, beta;  "step": gates [rows, 2 heads] = g, dt with dt = softplus(a + dt_bias);
+    "delta_channel": gates [rows, heads + heads * D] = beta, then g per key channel made from `decay_in`
+    [rows, heads * D] and dt_bias [heads * D].  The request's slot read and the slot written must differ (a step reads
+    one and writes its spare)."""
+    _cuda(proj, taps_w, ready, a_log, dt_bias, gates, state, bias, decay_in)
     rows = proj.shape[0]
     taps = taps_w.shape[1]
-    _need(proj.dtype == torch.float32 and proj.dim() == 2 and proj.shape[1] >= channels, "conv_prepare: projections float32 [rows, >= channels]")
+    kind = ("delta", "step", "delta_channel").index(gate_kind)
+    _need(proj.dtype == torch.float32 and proj.dim() == 2 and proj.shape[1] >= first + channels, "conv_prepare: projections float32 [rows, >= channels]")
     _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (channels, taps), "conv_prepare: taps float32 [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == channels), "conv_prepare: bias float32 [channels]")
     _need(ready.dtype == torch.float32 and tuple(ready.shape) == (rows, channels), "conv_prepare: output shape does not fit")
-    _need(gates.dtype == torch.float32 and tuple(gates.shape) == (rows, 2 * heads), "conv_prepare: gates float32 [rows, 2 heads]")
-    _need(a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == heads and dt_bias.numel() == heads,
-          "conv_prepare: A_log and dt_bias float32 [heads]")
-    _need(max(b_off, a_off) + heads <= proj.shape[1], "conv_prepare: gate columns outside the projections")
+    per_row = heads + heads * key_dim if kind == 2 else 2 * heads
+    _need(gates.dtype == torch.float32 and tuple(gates.shape) == (rows, per_row), "conv_prepare: gates float32 of the kind's width")
+    _need(a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == heads
+          and dt_bias.numel() == (heads * key_dim if kind == 2 else heads), "conv_prepare: A_log [heads] and dt_bias float32")
+    _need((kind == 2 or a_off + heads <= proj.shape[1]) and (kind == 1 or b_off + heads <= proj.shape[1]),
+          "conv_prepare: gate columns outside the projections")
+    ds = 0
+    if kind == 2:
+        _need(decay_in is not None and decay_in.dtype == torch.float32 and tuple(decay_in.shape) == (rows, heads * key_dim),
+              "conv_prepare: decay_in float32 [rows, heads * D]")
+        ds = decay_in.shape[1]
     _need(state.dtype == torch.float32 and state.dim() == 2 and conv_off + (taps - 1) * channels <= state.shape[1],
           "conv_prepare: state slots too small")
     _check(_fn("recurrence", "llmx_conv_prepare")(
-        _ptr(proj), proj.shape[1], channels, q_channels, k_channels, _ptr(taps_w), taps, _ptr(ready), _ptr(a_log), _ptr(dt_bias),
-        int(b_off), int(a_off), _ptr(gates), heads, key_dim, float(q_factor), _ptr(state), state.shape[1], int(conv_off),
-        _ptr(step.row_request), _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots),
-        _ptr(step.state_slots_out), rows, step.requests, _stream()), "conv_prepare")
+        _ptr(proj), proj.shape[1], int(first), channels, q_channels, k_channels, _ptr(taps_w), _ptr(bias), taps, _ptr(ready),
+        _ptr(a_log), _ptr(dt_bias), int(b_off), int(a_off), kind, _ptr(decay_in), ds, _ptr(gates), gates.shape[1], heads, key_dim,
+        float(q_factor), _ptr(state), state.shape[1], int(conv_off), _ptr(step.row_request), _ptr(step.row_start),
+        _ptr(step.row_count), _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out), rows, step.requests,
+        _stream()), "conv_prepare")
+
+
+# ---------------------------------------------------------------------------
+# Softmax attention over [key ; value] rows; experts chosen by a table.
+def qk_norm_rope_write(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       freq: Optional[torch.Tensor], positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor,
+                       cache: torch.Tensor) -> None:
+    """Rows of the stacked product [q (heads * D) | k (kv_heads * D) | v (kv_heads * V)], float32: per-head RMS norm of q
+    and k (weights [D] or None), rotation of the first 2 * len(freq) values of each q and k head (value i with value
+    i + len(freq), angle position * freq[i]), queries to q_out [rows, heads * D], [k ; v] to cache [pages, 1, kv_heads,
+    page, D + V] at the rows' slots."""
+    _cuda(proj, q_weight, k_weight, freq, positions, slots, q_out, cache)
+    rows = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.shape[1] == (heads + kv_heads) * key_dim + kv_heads * value_dim, "qk_write: product width does not fit")
+    _need(tuple(q_out.shape) == (rows, heads * key_dim), "qk_write: q_out shape does not fit")
+    _need(cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == kv_heads and cache.shape[4] == key_dim + value_dim,
+          "qk_write: cache layout does not fit")
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == key_dim), "qk_write: norm weight float32 [D]")
+    half = 0 if freq is None else freq.numel()
+    _need(freq is None or freq.dtype == torch.float32, "qk_write: frequencies float32")
+    _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= rows and slots.numel() >= rows,
+          "qk_write: positions and slots must be int32 per row")
+    _check(_fn("attention_split", "llmx_qk_norm_rope_write")(
+        _ptr(proj), proj.shape[1], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(freq), half, _ptr(positions), _ptr(slots),
+        _ptr(q_out), _code(q_out), _ptr(cache), _code(cache), rows, heads, kv_heads, key_dim, value_dim, cache.shape[3],
+        _stream()), "qk_norm_rope_write")
+
+
+def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
+                    positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
+                    value_dim: int, window: Optional[int], chunk: Optional[int], scale: float) -> torch.Tensor:
+    """Paged softmax attention, one block per (row, head); q [rows, heads * D] and out [rows, heads * V] of one type;
+    cache [pages, 1, kv_heads, page, D + V].  A row at position p reads keys max(p - window + 1, floor(p / chunk) * chunk,
+    0) .. p."""
+    _cuda(q, cache, out, row_request, positions, block_tables)
+    rows = q.shape[0]
+    _need(q.shape[1] == heads * key_dim and tuple(out.shape) == (rows, heads * value_dim) and q.dtype == out.dtype,
+          "attention: q and out shapes do not fit")
+    _need(cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == kv_heads and cache.shape[4] == key_dim + value_dim,
+          "attention: cache layout does not fit")
+    for t in (row_request, positions, block_tables):
+        _need(t.dtype == torch.int32, "attention: metadata must be int32")
+    _need(block_tables.dim() == 2 and row_request.numel() >= rows and positions.numel() >= rows, "attention: metadata shapes do not fit")
+    _check(_fn("attention_split", "llmx_attention_split")(
+        _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
+        block_tables.shape[1], rows, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0), int(chunk or 0),
+        float(scale), _stream()), "attention_split")
+    return out
+
+
+def moe_tiles_len(pairs: int, experts: int) -> int:
+    return 2 + 2 * ((pairs + 31) // 32 + experts)
+
+
+def moe_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, lists: torch.Tensor, counts: torch.Tensor,
+              tiles: torch.Tensor) -> None:
+    """Sort the step's (row, k) pairs by the expert the table gives them: lists int32 [experts, rows * top] (pairs in
+    order), counts int32 [experts], tiles int32 [moe_tiles_len] (their number, then (expert, first place) of every tile
+    of 32 pairs)."""
+    _cuda(token_ids, table, lists, counts, tiles)
+    rows, (vocab, top) = token_ids.numel(), table.shape
+    for t in (token_ids, table, lists, counts, tiles):
+        _need(t.dtype == torch.int32, "moe_route: int32 tensors")
+    _need(lists.numel() >= experts * rows * top and counts.numel() >= experts and tiles.numel() >= moe_tiles_len(rows * top, experts),
+          "moe_route: outputs too small")
+    _check(_fn("moe", "llmx_moe_route")(_ptr(token_ids), _ptr(table), top, rows, experts, vocab, _ptr(lists), _ptr(counts),
+                                        _ptr(tiles), _stream()), "moe_route", 2)
+
+
+def moe_product(a: torch.Tensor, a_div: int, w: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor, tiles: torch.Tensor,
+                pairs: int, out: torch.Tensor, gated: bool, tensor_cores: bool = True) -> torch.Tensor:
+    """out[pair] = a[pair // a_div] W_e^T for the expert e whose list holds the pair; w [experts, N (gated: 2 N, gate rows
+    then up rows), K] of a's type.  gated: out = silu(gate) * up in out's type; else float32."""
+    _cuda(a, w, lists, counts, tiles, out)
+    experts, wn, K = w.shape
+    N = wn // 2 if gated else wn
+    _need(a.dtype == w.dtype and a.dim() == 2 and a.shape[1] == K and a.shape[0] * a_div >= pairs, "moe_product: rows do not fit the weights")
+    _need(tuple(out.shape) == (pairs, N), "moe_product: output shape does not fit")
+    _check(_fn("moe", "llmx_moe_product")(_ptr(a), int(a_div), _ptr(w), _code(w), _ptr(lists), _ptr(counts), _ptr(tiles), pairs,
+                                          experts, _ptr(out), _code(out), N, K, 1 if gated else 0, 1 if tensor_cores else 0,
+                                          _stream()), "moe_product")
+    return out
+
+
+def moe_combine_(x: torch.Tensor, y: torch.Tensor, top: int, weight: float) -> torch.Tensor:
+    """x[row] += weight * sum_k y[row * top + k], k in increasing order; float32."""
+    _cuda(x, y)
+    rows, width = x.shape
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and tuple(y.shape) == (rows * top, width), "moe_combine: shapes do not fit")
+    _check(_fn("moe", "llmx_moe_combine")(_ptr(y), _ptr(x), rows, top, width, float(weight), _stream()), "moe_combine")
+    return x
 
 
 # ---------------------------------------------------------------------------

@@ -4,13 +4,17 @@ from .linear import Linear
 from .norm import LayerNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 from .attention import Attention
-from .mlp import ClampedGLU, GatedMLP
+from .mlp import ClampedGLU, GatedMLP, TableRoutedExperts
 from .block import ParallelBlock, PreNormBlock
 from .linear_attention import DecayedLinearAttention
 from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
 from .embedding import LogitsHead, TokenEmbedding
+from .state_space import SelectiveStateSpace
+from .masked_attention import MaskedAttention
+from .mixer_pair import MixerPair
 
 __all__ = ["GroupView", "Part", "Precision", "StepBatch", "Linear", "RMSNorm", "NoPositionEncoding",
            "RotaryEmbedding", "Attention", "GatedMLP", "PreNormBlock", "LogitsHead", "TokenEmbedding", "LayerNorm", "ClampedGLU",
-           "ParallelBlock", "DecayedLinearAttention", "GatedDeltaRule", "LatentAttention"]
+           "ParallelBlock", "DecayedLinearAttention", "GatedDeltaRule", "LatentAttention",
+           "TableRoutedExperts", "SelectiveStateSpace", "MaskedAttention", "MixerPair"]

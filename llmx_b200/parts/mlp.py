@@ -18,23 +18,25 @@ from .linear import Linear, call_struct, stored_product
 
 
 class GatedMLP(Part):
-    def __init__(self, hidden: int, intermediate: int, activation: str = "silu"):
+    def __init__(self, hidden: int, intermediate: int, activation: str = "silu",
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        """`names`: the roles of the gate, up and down weights."""
         if activation != "silu":
             raise ValueError(f"activation {activation!r} has no kernel here (silu)")
         self.hidden, self.intermediate, self.activation = int(hidden), int(intermediate), activation
+        self.names = tuple(names)
         self._native: Optional[NativeHandle] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {
-            "gate_proj.weight": TensorSpec((self.intermediate, self.hidden)),
-            "up_proj.weight": TensorSpec((self.intermediate, self.hidden)),
-            "down_proj.weight": TensorSpec((self.hidden, self.intermediate)),
-        }
+        g, u, d = self.names
+        return {g: TensorSpec((self.intermediate, self.hidden)), u: TensorSpec((self.intermediate, self.hidden)),
+                d: TensorSpec((self.hidden, self.intermediate))}
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
-        self.gate_up = Linear(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0), precision)
-        self.down = Linear(tensors["down_proj.weight"], precision)
+        g, u, d = self.names
+        self.gate_up = Linear(torch.cat([tensors[g], tensors[u]], dim=0), precision)
+        self.down = Linear(tensors[d], precision)
         self._native = None
 
     @property
@@ -101,3 +103,64 @@ class ClampedGLU(Part):
         act = torch.empty((rows, self.intermediate), dtype=self.precision.act, device=h.device)
         ops.clamped_glu(gu, act, self.limit, self.alpha)
         self.down(act, out=residual, accumulate=True)
+
+
+class TableRoutedExperts(Part):
+    """A mixture of experts without a router: an integer table [vocab, top] gives each token id its `top` experts
+    (the entries of a row differ), each weighing 1 / top.
+        residual += (1 / top) * sum over the token's experts e of (silu(h Wg_e^T) * (h Wu_e^T)) Wd_e^T  [+ shared(h)]
+    `shared`: a feed-forward part that runs for every token beside the experts (or None).  The experts' weights are
+    stacked ([experts, 2 ff, E] gate rows then up rows, and [experts, E, ff]); the step's (row, expert) pairs are sorted
+    by expert on the device and the products run a tile of one expert's pairs at a time (csrc/moe.cu), so nothing of
+    the routing is read on the host.  Tensor roles: `table`, `e<i>.gate|up|down`; the shared part's under `shared.`."""
+
+    def __init__(self, hidden: int, vocab: int, experts: int, top: int, intermediate: int, shared: Optional[Part] = None,
+                 names=("gate", "up", "down"), table_role: str = "table", shared_name: str = "shared"):
+        if not 1 <= top <= experts:
+            raise ValueError("experts: a token uses between one and all of the experts")
+        self.hidden, self.vocab, self.experts, self.top = int(hidden), int(vocab), int(experts), int(top)
+        self.intermediate, self.shared, self.names = int(intermediate), shared, tuple(names)
+        self.table_role, self.shared_name = table_role, shared_name
+
+    def children(self) -> Dict[str, Part]:
+        return {} if self.shared is None else {self.shared_name: self.shared}
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        g, u, d = self.names
+        specs = {self.table_role: TensorSpec((self.vocab, self.top), "int_table", init="distinct_rows", bound=self.experts)}
+        for e in range(self.experts):
+            specs[f"e{e}.{g}"] = TensorSpec((self.intermediate, self.hidden))
+            specs[f"e{e}.{u}"] = TensorSpec((self.intermediate, self.hidden))
+            specs[f"e{e}.{d}"] = TensorSpec((self.hidden, self.intermediate))
+        return specs
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        g, u, d = self.names
+        self.table = tensors[self.table_role].to(torch.int32).contiguous()
+        if int(self.table.min()) < 0 or int(self.table.max()) >= self.experts:
+            raise ValueError(f"experts: the table names an expert outside 0..{self.experts - 1}")
+        act = precision.act
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.{g}"], tensors[f"e{e}.{u}"]], dim=0) for e in range(self.experts)]).to(act).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.{d}"] for e in range(self.experts)]).to(act).contiguous()
+
+    def forward(self, h: torch.Tensor, step: StepBatch, residual: torch.Tensor) -> None:
+        from .. import ops
+        rows = h.shape[0]
+        if not (h.is_cuda and h.is_contiguous() and h.dtype is self.precision.act and tuple(h.shape) == (rows, self.hidden)
+                and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
+            raise runtime.KernelError("experts: rows of the path's type and the part's width, a float32 residual")
+        pairs = rows * self.top
+        dev = h.device
+        lists = torch.empty((self.experts, pairs), dtype=torch.int32, device=dev)
+        counts = torch.empty((self.experts,), dtype=torch.int32, device=dev)
+        tiles = torch.empty((ops.moe_tiles_len(pairs, self.experts),), dtype=torch.int32, device=dev)
+        ops.moe_route(step.token_ids, self.table, self.experts, lists, counts, tiles)
+        tc = not self.precision.invariant
+        act = torch.empty((pairs, self.intermediate), dtype=self.precision.act, device=dev)
+        ops.moe_product(h, self.top, self.w_gate_up, lists, counts, tiles, pairs, act, gated=True, tensor_cores=tc)
+        y = torch.empty((pairs, self.hidden), dtype=torch.float32, device=dev)
+        ops.moe_product(act, 1, self.w_down, lists, counts, tiles, pairs, y, gated=False, tensor_cores=tc)
+        ops.moe_combine_(residual, y, self.top, 1.0 / self.top)
+        if self.shared is not None:
+            self.shared.forward(h, step, residual)

@@ -1,7 +1,10 @@
 """Norms.  RMSNorm: y = x * (rsqrt(mean(x^2) + eps) * w), 32-bit arithmetic.
 
 The weight is the plain `w` (not `1 + w`), as the reference computes this
-architecture (src/backends/cpu/cpu_backend.hpp:1437-1459).
+architecture (src/backends/cpu/cpu_backend.hpp:1437-1459).  `one_plus=True` is the
+norm of designs that store the weight around zero: y = x * rsqrt(...) * (1 + w);
+the sum 1 + w is made once at load, in 32-bit.  `role` names the weight's tensor
+("" names it by the part's prefix alone).
 """
 from __future__ import annotations
 
@@ -17,17 +20,21 @@ from .linear import bare_step
 
 
 class RMSNorm(Part):
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = int(width), float(eps)
+    def __init__(self, width: int, eps: float, role: str = "weight", one_plus: bool = False):
+        self.width, self.eps, self.role, self.one_plus = int(width), float(eps), role, bool(one_plus)
         self.weight: Optional[torch.Tensor] = None
         self._native: Optional[NativeHandle] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
+        if self.one_plus:
+            return {self.role: TensorSpec((self.width,), "vector", init="normal", std=0.05)}
+        return {self.role: TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
-        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.role].to(torch.float32).contiguous()
+        if self.one_plus:
+            self.weight = (self.weight + 1.0).contiguous()
         self._native = None
 
     @property

@@ -42,7 +42,7 @@ def check_tensors(specs: Mapping[str, TensorSpec], source, where: str,
         if n not in have:
             continue
         shape, dtype = tuple(source.shape(n)), source.dtype(n)
-        if shape != tuple(s.shape):
+        if len(shape) != len(s.shape) or any(want >= 0 and have_ != want for have_, want in zip(shape, s.shape)):   # -1: a size the part reads from the tensor
             wrong.append((n, f"shape {list(shape)}, expected {list(s.shape)}"))
         elif s.kind == "int_table" and dtype not in _INTS:
             wrong.append((n, f"type {dtype}, expected an integer type"))

@@ -94,7 +94,16 @@ class RandomSource:
         stream = _stream_seed(self.seed, name)
         count = 1
         for d in s.shape:
+            if int(d) < 0:
+                raise ValueError(f"{name}: a size that only stored tensors give; random weights need it named in the configuration")
             count *= int(d)
+        if s.kind == "int_table" and s.init == "distinct_rows":
+            # Row r: the first `width` of the values 0 .. bound-1 in the order of a hash of (r, value).
+            rows, width = int(s.shape[0]), int(s.shape[1])
+            i = torch.arange(rows * s.bound, dtype=torch.int64, device=self.device)
+            keys = _mix64(torch.tensor(stream, dtype=torch.int64, device=self.device) + i * -7046029254386353131)
+            order = torch.argsort(keys.reshape(rows, s.bound), dim=1, stable=True)
+            return order[:, :width].to(torch.int32).contiguous()
         if s.kind == "int_table":
             i = torch.arange(count, dtype=torch.int64, device=self.device)
             h = _mix64(torch.tensor(stream, dtype=torch.int64, device=self.device) + i * -7046029254386353131)

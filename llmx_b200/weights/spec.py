@@ -13,13 +13,15 @@ class TensorSpec:
           "table"   [rows, width] gathered by id (an embedding)
           "vector"  a norm's weight; held in 32-bit on the device whatever the file stores
           "int_table" integer table, held as int32
-    init: how the random-weights mode fills it: "normal" (N(0, std)) or "one_plus_normal" (1 + N(0, std)).
+    init: how the random-weights mode fills it: "normal" (N(0, std)) or "one_plus_normal" (1 + N(0, std)); for an
+          integer table also "distinct_rows": every row holds different values below `bound`.
     """
     shape: Tuple[int, ...]
     kind: str = "matrix"
     optional: bool = False
     init: str = "normal"
     std: float = 0.02
+    bound: int = 0
 
 
 class WeightError(ValueError):

@@ -117,8 +117,6 @@ def read_header(path: str) -> Tuple[Dict[str, TensorEntry], Dict[str, str]]:
         if off[1] - off[0] != count * width:
             raise SafetensorsError(
                 f"{path}: tensor {name!r}: offsets span {off[1] - off[0]} bytes, shape {shape} of {e['dtype']} needs {count * width}")
-        if off[0] % width:
-            raise SafetensorsError(f"{path}: tensor {name!r}: data is not aligned to its element size")
         entries[name] = TensorEntry(name, dtype, tuple(shape), base + off[0], base + off[1], path)
     # No gaps, no overlaps, and the data ends where the file ends.
     at = base
@@ -148,6 +146,10 @@ class SafetensorsFile:
             count *= d
         if count == 0:
             return torch.empty(e.shape, dtype=e.dtype)
+        if e.begin % torch.empty((), dtype=e.dtype).element_size():
+            # Data that does not start on a multiple of its element size (an integer table after an odd number of
+            # 16-bit values, a header of odd length): copied out, so that no reader meets an unaligned address.
+            return torch.frombuffer(bytearray(self._map[e.begin:e.end]), dtype=e.dtype, count=count).view(e.shape)
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")  # the mapping is read-only; the tensor is never written
             t = torch.frombuffer(self._map, dtype=e.dtype, count=count, offset=e.begin)
@@ -228,12 +230,13 @@ class TensorDirectory:
 
 
 def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor], metadata: Optional[Mapping[str, str]] = None) -> None:
-    """Write CPU tensors to `path` in name order, contiguous, no gaps."""
+    """Write CPU tensors to `path`, contiguous, no gaps: wider element types first, then in name order, so that every
+    tensor starts on a multiple of its element size."""
     header: Dict[str, object] = {}
     if metadata:
         header["__metadata__"] = dict(metadata)
     at = 0
-    order = sorted(tensors)
+    order = sorted(tensors, key=lambda n: (-tensors[n].element_size(), n))
     for name in order:
         t = tensors[name]
         if t.dtype not in _NAMES:

@@ -1,0 +1,449 @@
+"""Kisepel on the GPU against the plain implementation (tests/plain_kisepel.py): every mechanism alone, whole models
+under every cutting, the edges of chunks and pages, slots used again, long decoding, generation through the scheduler.
+
+The configurations are this file's own: sizes that differ from one another everywhere (head counts, key / value /
+state widths, groups, ranks, chunks, filter lengths, expert counts, layers without a feed-forward, without a shared
+expert, without a chunk, with only part of a head rotated, loops over a part of the layers), and weights scaled up
+so that activations are of order one and attention is far from uniform.
+"""
+import copy
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_kisepel as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def moe(experts=5, top=2, ff=24, shared=40):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": None if shared is None else {"ff": shared}}
+
+
+MOE = moe()
+
+
+def lightning(heads=3, dim=20, vdim=12, decay=(1.0, 0.97, 0.6), mlp=MOE):
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}, "mlp": mlp}
+
+
+def mamba(heads=6, vdim=8, state=12, groups=3, conv=4, norm_groups=2, mlp=MOE):
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}, "mlp": mlp}
+
+
+def parallel(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.3, chunk=20, rot_dims=8, base=10000.0, factor=2.0,
+             r_heads=4, r_kv_heads=2, r_dim=12, r_vdim=20, conv=3, decay_rank=7, gate_rank=5, mlp=MOE):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale,
+            "rot": {"base": base, "dims": rot_dims, "scaling": {"factor": factor}}}
+    if chunk is not None:
+        left["mask"] = {"size": chunk}
+    right = {"heads": r_heads, "kv_heads": r_kv_heads, "dim": r_dim, "vdim": r_vdim, "conv": conv, "decay_rank": decay_rank, "gate_rank": gate_rank}
+    return {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+
+
+def config(layers, width=96, vocab=200, eps=1e-5, emb=3.0, logit=0.5, loop=None):
+    c = {"architecture": "Kisepel", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": emb},
+         "logit_scale": logit, "layers": layers}
+    if loop is not None:
+        c["loop"] = dict(zip(("start", "stop", "times"), loop))
+    return c
+
+
+# Two whole models.  P: every mixer kind with different sizes, the middle three layers run three times, one layer
+# without a feed-forward, one without a shared expert, one expert a token and all experts a token.
+MODEL_P = config([mamba(), parallel(), lightning(mlp=None), mamba(heads=2, vdim=20, state=6, groups=1, conv=2, norm_groups=1, mlp=moe(3, 1, 16, None)),
+                  parallel(heads=3, kv_heads=3, dim=24, vdim=8, scale=0.25, chunk=7, rot_dims=24, factor=1.0, r_heads=2, r_kv_heads=1, r_dim=20,
+                           r_vdim=10, conv=2, decay_rank=3, gate_rank=9, mlp=moe(4, 4, 12, 20)),
+                  lightning(heads=2, dim=36, vdim=40, decay=(0.999, 0.9), mlp=moe(7, 3, 30, 50))], loop=(1, 4, 3))
+# Q: a width and a vocabulary that are no multiples of 8 (products off the tensor cores), one head, a chunk of one page,
+# the whole model run twice, no rotation on one side.
+MODEL_Q = config([parallel(heads=1, kv_heads=1, dim=10, vdim=14, scale=0.5, chunk=8, rot_dims=0, r_heads=3, r_kv_heads=1, r_dim=10, r_vdim=6,
+                           conv=5, decay_rank=4, gate_rank=4, mlp=moe(2, 1, 30, 11)),
+                  lightning(heads=1, dim=9, vdim=7, decay=(0.8,), mlp=None), mamba(heads=3, vdim=6, state=5, groups=3, conv=1, norm_groups=3, mlp=moe(6, 2, 10, None))],
+                 width=50, vocab=101, eps=1e-6, emb=1.0, logit=2.0, loop=(0, 3, 2))
+
+
+def make_folder(tmp, cfg, seed, dtype=torch.float32, gain=5.0, sharpen=1.0, mute_right=False, open_ranks=False):
+    """A model folder with random weights of order one: matrices N(0, 0.02) x gain (query maps x sharpen on top).
+    `mute_right`: the right side of every pair of mixers gets a zero output weight, so that the attention side is
+    seen alone.  `open_ranks`: the configuration written does not name the low-rank pairs' ranks."""
+    from llmx_b200.config import KisepelConfig
+    from llmx_b200.registry import architecture_of
+    from llmx_b200.weights import RandomSource, write_safetensors
+    c = KisepelConfig.from_dict(cfg)
+    model = architecture_of(cfg).build(c)
+    specs = model.tensor_specs()
+    src = RandomSource(specs, seed, dtype=torch.float32)
+    tensors = {}
+    for n in src.names():
+        t = src.tensor(n)
+        if specs[n].kind in ("matrix", "table") and not n.endswith("conv") and not n.endswith((".a2", ".g2")):
+            t = t * gain
+        if n.endswith("left.q"):
+            t = t * sharpen
+        if mute_right and n.endswith("right.out"):
+            t = t * 0.0
+        tensors[n] = t if specs[n].kind == "int_table" else t.to(dtype)
+    os.makedirs(tmp, exist_ok=True)
+    written = copy.deepcopy(cfg)
+    if open_ranks:
+        for layer in written["layers"]:
+            if layer["type"] == "parallel":
+                del layer["mixer"]["right"]["decay_rank"], layer["mixer"]["right"]["gate_rank"]
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(written, f)
+    write_safetensors(os.path.join(tmp, "model.safetensors"), tensors)
+    return {n: t.to(torch.float32).numpy() if specs[n].kind != "int_table" else t.numpy() for n, t in tensors.items()}
+
+
+def engine_of(folder, dtype, kv_tokens, page=4, requests=4):
+    from llmx_b200.engine import Engine, EngineOptions
+    return Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page, max_requests=requests))
+
+
+def worst_error(got, refs):
+    worst, where = 0.0, None
+    for key, row in got.items():
+        d = float(np.abs(row - refs[key[0]][key[1]]).max())
+        if not np.isfinite(d):
+            return float("inf"), key
+        if d > worst:
+            worst, where = d, key
+    return worst, where
+
+
+CUTTINGS = (helpers.trace_whole, helpers.trace_tail_decoded, helpers.trace_portions, helpers.trace_mixed)
+
+
+def run_cuttings(folder, cfg, w, dtype, lengths, tol, page=4, seed=0):
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab"], n, seed=seed + i) for i, n in enumerate(lengths)}
+    refs = {rid: plain.forward(cfg, w, ids) for rid, ids in requests.items()}
+    scale = max(float(np.abs(r).max()) for r in refs.values())
+    measured = {}
+    for make in CUTTINGS:
+        steps = make(requests)
+        engine = engine_of(folder, dtype, helpers.tokens_needed(steps), page)
+        got = helpers.run_trace(engine, steps)
+        engine.cache.check()
+        assert all(u == 0 for u in engine.cache.used_pages())
+        assert engine.cache.state_slots.free_slots == engine.cache.state_slots.num_slots
+        worst, where = worst_error(got, refs)
+        measured[make.__name__] = worst / scale
+        assert len(got) == sum(lengths)
+        assert worst <= tol * scale, f"{make.__name__}: {worst:.3e} at {where} (scale {scale:.3f})"
+    return measured
+
+
+# ---- every mechanism alone: one-layer models -----------------------------------------------------------------------
+ONE_LAYER = {
+    "lightning": lightning(),
+    "mamba": mamba(mlp=None),
+    "mamba_one_group_one_tap_one_norm": mamba(heads=4, vdim=10, state=7, groups=1, conv=1, norm_groups=1, mlp=None),
+    "mamba_groups_are_heads_long_filter": mamba(heads=3, vdim=4, state=40, groups=3, conv=6, norm_groups=3, mlp=None),
+    "mamba_wide_state": mamba(heads=2, vdim=12, state=160, groups=2, conv=3, norm_groups=4, mlp=None),
+    "parallel": parallel(mlp=None),
+    "parallel_values_narrower_than_keys": parallel(heads=6, kv_heads=2, dim=40, vdim=8, chunk=33, rot_dims=16, r_heads=6, r_kv_heads=6, r_dim=8, r_vdim=5, conv=2, mlp=None),
+    "parallel_one_kv_head_full_rotation_no_chunk": parallel(heads=4, kv_heads=1, dim=12, vdim=12, chunk=None, rot_dims=12, factor=1.0, r_heads=3, r_kv_heads=1,
+                                                            r_dim=36, r_vdim=4, conv=1, decay_rank=1, gate_rank=2, mlp=None),
+    "parallel_chunk_of_one": parallel(heads=2, kv_heads=2, dim=8, vdim=8, chunk=1, rot_dims=4, mlp=None),
+    "parallel_wide_heads": parallel(heads=2, kv_heads=1, dim=160, vdim=72, chunk=50, rot_dims=64, r_heads=2, r_kv_heads=1, r_dim=136, r_vdim=6, mlp=None),
+    "experts_one_of_many": lightning(mlp=moe(9, 1, 20, None)),
+    "experts_all_of_them_with_shared": lightning(mlp=moe(3, 3, 50, 10)),
+    "experts_wide": lightning(mlp=moe(4, 2, 136, 72)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ONE_LAYER))
+def test_one_mixer_under_every_cutting_float32(tmp_path, name):
+    cfg = config([ONE_LAYER[name]])
+    w = make_folder(str(tmp_path), cfg, seed=7)
+    run_cuttings(str(tmp_path), cfg, w, "float32", [50, 3, 77, 20, 1, 64], 1e-4)
+
+
+def test_row_kernels_against_the_plain_functions():
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    # The gated norm with the gate before the norm, in parts of a row, against gate-after on the same inputs.
+    o = torch.randn(4, 60, generator=g)
+    wide = torch.randn(4, 100, generator=g)
+    gate = wide[:, 30:90].numpy().astype(np.float64)
+    for group, kind in ((60, "silu"), (12, "silu"), (20, "sigmoid")):
+        wt = torch.rand(60, generator=g) + 0.5
+        out = torch.empty(4, 60, dtype=torch.float32, device=DEV)
+        ops.gated_rmsnorm(o.to(DEV), wide.to(DEV)[:, 30:90], wt.to(DEV), 1e-5, group, kind, out, gate_first=True)
+        z = o.numpy().astype(np.float64) * (plain.silu(gate) if kind == "silu" else plain.sigmoid(gate))
+        ref = plain.rms_norm(z.reshape(4, 60 // group, group), None, 1e-5).reshape(4, 60) * wt.numpy()
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5
+        after = torch.empty(4, 60, dtype=torch.float32, device=DEV)
+        ops.gated_rmsnorm(o.to(DEV), wide.to(DEV)[:, 30:90], wt.to(DEV), 1e-5, group, kind, after)
+        assert np.abs(after.cpu().numpy() - ref).max() > 1e-2          # the two orders are different functions
+    # Two normed rows added into a third.
+    for width in (50, 96, 1030):
+        a, b, x = (torch.randn(5, width, generator=g) * s for s in (3.0, 0.1, 1.0))
+        wa, wb = torch.rand(width, generator=g) + 0.5, torch.rand(width, generator=g) - 0.5
+        got = ops.pair_norm_add_(x.clone().to(DEV), a.to(DEV), b.to(DEV), wa.to(DEV), wb.to(DEV), 1e-5, 0.5).cpu().numpy()
+        ref = x.numpy() + 0.5 * (plain.rms_norm(a.numpy(), wa.numpy(), 1e-5) + plain.rms_norm(b.numpy(), wb.numpy(), 1e-5))
+        assert np.abs(got - ref).max() <= 1e-5
+    x, y = torch.randn(7, 33, generator=g), torch.randn(7, 33, generator=g)
+    assert torch.equal(ops.add_(x.clone().to(DEV), y.to(DEV)).cpu(), x + y)
+    # The norm with a weight stored around zero is the norm with the weight plus one.
+    from llmx_b200.parts import Precision, RMSNorm
+    norm = RMSNorm(40, 1e-6, role="", one_plus=True)
+    wz = torch.randn(40, generator=g) * 0.2
+    norm.load({"": wz.to(DEV)}, Precision.of("float32"))
+    xs = torch.randn(3, 40, generator=g) * 4
+    assert np.abs(norm.forward(xs.to(DEV)).cpu().numpy() - plain.rms_norm(xs.numpy(), wz.numpy(), 1e-6, one_plus=True)).max() <= 1e-5
+
+
+@pytest.mark.parametrize("rows,experts,top,K,N", [(1, 4, 2, 64, 40), (37, 5, 3, 96, 72), (300, 3, 1, 160, 136), (64, 8, 8, 32, 8)])
+def test_expert_products_on_the_tensor_cores_equal_those_on_the_cuda_cores(rows, experts, top, K, N):
+    """The grouped products of the experts in bfloat16: tensor-core tiles against the CUDA-core kernel (the same
+    bfloat16 inputs, 32-bit sums), and both against a plain loop over the pairs; tiles that are full, partial, and
+    experts that get no pair at all."""
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    vocab = 50
+    pool = experts - 1 if top < experts else experts          # where there is room, the last expert gets no pair at all
+    table = torch.stack([torch.randperm(pool, generator=g)[:top] for _ in range(vocab)]).to(torch.int32)
+    ids = torch.randint(0, vocab, (rows,), generator=g).to(torch.int32)
+    h = (torch.randn(rows, K, generator=g)).to(torch.bfloat16)
+    w_gu = (torch.randn(experts, 2 * N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    w_d = (torch.randn(experts, K, N, generator=g) * N ** -0.5).to(torch.bfloat16)
+    pairs = rows * top
+    lists = torch.empty((experts, pairs), dtype=torch.int32, device=DEV)
+    counts = torch.empty((experts,), dtype=torch.int32, device=DEV)
+    tiles = torch.empty((ops.moe_tiles_len(pairs, experts),), dtype=torch.int32, device=DEV)
+    ops.moe_route(ids.to(DEV), table.to(DEV), experts, lists, counts, tiles)
+    cnt = counts.cpu().numpy()
+    assert cnt.sum() == pairs and int(tiles[0]) == sum(-(-int(c) // 32) for c in cnt)
+    for e in range(experts):
+        mine = lists[e, :cnt[e]].cpu().numpy()
+        assert list(mine) == sorted(mine) and all(int(table[ids[p // top], p % top]) == e for p in mine)
+    results = []
+    for tc in (True, False):
+        act = torch.full((pairs, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.moe_product(h.to(DEV), top, w_gu.to(DEV), lists, counts, tiles, pairs, act, gated=True, tensor_cores=tc)
+        y = torch.full((pairs, K), 7.0, dtype=torch.float32, device=DEV)
+        ops.moe_product(act, 1, w_d.to(DEV), lists, counts, tiles, pairs, y, gated=False, tensor_cores=tc)
+        results.append((act.float().cpu().numpy(), y.cpu().numpy()))
+    ref_act = np.zeros((pairs, N))
+    for p in range(pairs):
+        e = int(table[ids[p // top], p % top])
+        hp = h[p // top].float().numpy().astype(np.float64)
+        ref_act[p] = plain.silu(hp @ w_gu[e, :N].float().numpy().T.astype(np.float64)) * (hp @ w_gu[e, N:].float().numpy().T.astype(np.float64))
+    for act, y in results:
+        assert np.abs(act - ref_act).max() <= 2 ** -7 * max(1.0, np.abs(ref_act).max())
+    assert np.abs(results[0][1] - results[1][1]).max() <= 2e-2 * np.abs(results[1][1]).max()      # the two act matrices differ by roundings to bfloat16
+    x = torch.zeros(rows, K, dtype=torch.float32, device=DEV)
+    ops.moe_combine_(x, torch.from_numpy(results[1][1]).to(DEV), top, 1.0 / top)
+    assert np.abs(x.cpu().numpy() - results[1][1].reshape(rows, top, K).sum(axis=1) / top).max() <= 1e-5
+
+
+# ---- whole models ----------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("which", ["P", "Q"])
+def test_whole_models_under_every_cutting_float32(tmp_path, which):
+    cfg = MODEL_P if which == "P" else MODEL_Q
+    w = make_folder(str(tmp_path), cfg, seed=11, open_ranks=which == "P")
+    run_cuttings(str(tmp_path), cfg, w, "float32", [50, 3, 77, 20, 1, 64, 133], 1e-4, page=4 if which == "P" else 8)
+
+
+# Twice the error measured when the budget was frozen, as a fraction of the logit scale (the plain implementation is
+# exact; the path rounds the inputs of products and the cached keys and values to bfloat16).
+BF16_BUDGET = {"P": 6e-2, "Q": 6e-2}
+
+
+@pytest.mark.parametrize("which", ["P", "Q"])
+def test_whole_models_under_every_cutting_bfloat16(tmp_path, which):
+    cfg = MODEL_P if which == "P" else MODEL_Q
+    w = make_folder(str(tmp_path), cfg, seed=11, dtype=torch.bfloat16)
+    measured = run_cuttings(str(tmp_path), cfg, w, "bfloat16", [50, 3, 77, 20, 1, 64, 133], BF16_BUDGET[which], page=16)
+    print("bfloat16 error / scale:", which, measured)
+
+
+def test_a_request_in_a_batch_equals_the_request_alone(tmp_path):
+    """Unequal requests in one step (a long portion, a short one, single tokens after history) against each alone."""
+    from llmx_b200.engine import StepEntry
+    cfg = MODEL_P
+    make_folder(str(tmp_path), cfg, seed=5)
+    ids = {r: helpers.random_ids(cfg["vocab"], n, seed=40 + i) for i, (r, n) in enumerate({"a": 90, "b": 31, "c": 12, "d": 2}.items())}
+    alone = {}
+    for r, t in ids.items():
+        e = engine_of(str(tmp_path), "float32", 256)
+        cut = len(t) // 2
+        e.step([StepEntry(r, t[:cut], [])])
+        alone[r] = e.step([StepEntry(r, t[cut:], list(range(len(t) - cut)))]).cpu().numpy()
+    e = engine_of(str(tmp_path), "float32", 512)
+    e.step([StepEntry(r, t[:len(t) // 2], []) for r, t in ids.items()])
+    got = e.step([StepEntry(r, t[len(t) // 2:], list(range(len(t) - len(t) // 2))) for r, t in ids.items()]).cpu().numpy()
+    at = 0
+    for r, t in ids.items():
+        n = len(t) - len(t) // 2
+        assert np.abs(got[at:at + n] - alone[r]).max() <= 1e-5 * np.abs(alone[r]).max(), r
+        at += n
+
+
+# ---- edges of chunks and pages -------------------------------------------------------------------------------------
+@pytest.mark.parametrize("chunk,page", [(20, 4), (16, 16), (33, 8), (300, 16)])
+def test_a_token_is_seen_exactly_inside_its_chunk(tmp_path, chunk, page):
+    """The attention side alone (the other side's output weight is zero): changing token j changes the logits from j
+    to the last position of j's chunk and leaves all others bit for bit as they were, in a prompt taken whole, in
+    portions that cut the chunk, and decoded; j and the chunk's edges lie at page borders and off them.  Pages below
+    the chunk in use have gone back to the pool."""
+    from llmx_b200.engine import StepEntry
+    cfg = config([parallel(chunk=chunk, mlp=None)])
+    make_folder(str(tmp_path), cfg, seed=3, sharpen=0.5, mute_right=True)        # flat attention: every key of the chunk carries weight
+    n = 2 * chunk + 13 if chunk < 100 else chunk + 40
+    base = helpers.random_ids(cfg["vocab"], n, seed=1)
+    for j in (0, chunk - 1, chunk, chunk + page, min(2 * chunk - 1, n - 2)):
+        other = list(base)
+        other[j] = (base[j] + 1) % cfg["vocab"]
+        end = min((j // chunk + 1) * chunk, n)                # the first position that must not see j
+        for how in ("whole", "portions", "decoded"):
+            rows = []
+            for ids in (base, other):
+                e = engine_of(str(tmp_path), "float32", 1024, page)
+                if how == "whole":
+                    out = e.step([StepEntry("r", ids, list(range(n)))]).cpu().numpy()
+                elif how == "portions":
+                    cuts, out, at = [max(end - 1, 1), 2, 1, 7], [], 0
+                    k = 0
+                    while at < n:
+                        p = max(1, min(cuts[k % 4], n - at))
+                        out.append(e.step([StepEntry("r", ids[at:at + p], list(range(p)))]).cpu().numpy())
+                        at, k = at + p, k + 1
+                    out = np.concatenate(out)
+                else:
+                    head = min(j + 3, n)
+                    out = [e.step([StepEntry("r", ids[:head], list(range(head)))]).cpu().numpy()]
+                    out += [e.step([StepEntry("r", [t], [0])]).cpu().numpy() for t in ids[head:]]
+                    out = np.concatenate(out)
+                e.cache.check()
+                held = e.cache.live["r"].tables[0].held_pages
+                assert held <= -(-(n - (n // chunk) * chunk) // page) + 1, (how, held)
+                rows.append(out)
+            a, b = rows
+            for i in range(j, end):
+                assert np.abs(a[i] - b[i]).max() > 1e-6 * np.abs(a).max(), (how, j, i, "a position of the chunk must see the token")
+            assert np.array_equal(a[end:], b[end:]), (how, j, "a token of another chunk was seen")
+            assert np.array_equal(a[:j], b[:j])
+
+
+def test_far_keys_inside_a_long_chunk(tmp_path):
+    """Attention over hundreds of keys across many pages, with a chunk edge in the middle: sharpened so that single far
+    keys decide; the recurrent layers carry everything from the start."""
+    cfg = config([parallel(chunk=512, rot_dims=4, factor=1.0, mlp=None), lightning(decay=(1.0, 0.999, 0.99)), mamba(mlp=None)])
+    w = make_folder(str(tmp_path), cfg, seed=9, sharpen=6.0)
+    run_cuttings(str(tmp_path), cfg, w, "float32", [700, 333], 1e-4, page=16)
+
+
+def test_slots_and_pages_used_again_start_from_nothing(tmp_path):
+    """Requests follow one another through the same two state slots and the same few pages; each equals the plain
+    implementation from its first token (which sees zeros before the start, whatever the slot held)."""
+    from llmx_b200.engine import StepEntry
+    cfg = MODEL_P
+    w = make_folder(str(tmp_path), cfg, seed=2)
+    e = engine_of(str(tmp_path), "float32", 64, page=4, requests=1)
+    for i in range(5):
+        ids = helpers.random_ids(cfg["vocab"], 40 + 5 * i, seed=90 + i)
+        ref = plain.forward(cfg, w, ids)
+        got = np.concatenate([e.step([StepEntry(i, ids[:3], [0, 1, 2])]).cpu().numpy(),
+                              e.step([StepEntry(i, ids[3:], list(range(len(ids) - 3)))]).cpu().numpy()])
+        e.end(i)
+        e.cache.check()
+        assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max(), i
+
+
+def test_long_decoding(tmp_path):
+    cfg = MODEL_Q
+    w = make_folder(str(tmp_path), cfg, seed=4)
+    ids = helpers.random_ids(cfg["vocab"], 400, seed=8)
+    ref = plain.forward(cfg, w, ids)
+    steps = helpers.trace_tail_decoded({"r": ids}, tail=390)
+    e = engine_of(str(tmp_path), "float32", 512, page=16)
+    got = helpers.run_trace(e, steps)
+    worst, where = worst_error(got, {"r": ref})
+    assert worst <= 1e-4 * np.abs(ref).max(), where
+
+
+# ---- the framework's entry points ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(tmp_path, dtype):
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    cfg = MODEL_P
+    w = make_folder(str(tmp_path), cfg, seed=6, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    prompts = [helpers.random_ids(cfg["vocab"], n, seed=n) for n in (5, 17, 33, 60)]
+    llm = LLM(str(tmp_path), dtype=dtype, kv_tokens=512, page_size=16, ubatch=24, max_seqs=3)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=24, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True))
+    assert [len(o.tokens) for o in outs] == [24] * 4
+    for p, o in zip(prompts, outs):
+        ids = list(p)
+        for t in o.tokens:
+            logits = plain.forward(cfg, w, ids)[-1]
+            best = int(np.argmax(logits))
+            gap = 2 * BF16_BUDGET["P"] if dtype == "bfloat16" else 1e-4
+            assert t == best or logits[best] - logits[t] <= gap * np.abs(logits).max(), (len(ids), t, best)
+            ids.append(t)
+    assert all(u == 0 for u in llm.engine.cache.used_pages())
+    assert llm.engine.cache.state_slots.free_slots == llm.engine.cache.state_slots.num_slots
+
+
+def test_recorded_steps_equal_plain_steps(tmp_path):
+    """Steps whose shape keeps coming are recorded as CUDA graphs and replayed (the routing of tokens to experts is
+    made on the device, so a recording holds for any tokens): the same logits as the plain implementation."""
+    from llmx_b200.engine import Engine, EngineOptions
+    cfg = MODEL_P
+    w = make_folder(str(tmp_path), cfg, seed=14)
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab"], n, seed=30 + i) for i, n in enumerate([70, 70, 70, 41])}
+    refs = {rid: plain.forward(cfg, w, ids) for rid, ids in requests.items()}
+    steps = helpers.trace_portions(requests, portions=[7, 7, 7, 7, 7, 7, 7, 7, 7, 1, 1, 1, 1, 1, 1, 1])
+    engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype="float32", kv_tokens=256, page_size=16, max_requests=2, record_after=1))
+    assert engine.model.recordable
+    got = helpers.run_trace(engine, steps, record=True)
+    assert len(engine.step_recordings) >= 2          # the portion of seven rows and the single row, at least
+    worst, where = worst_error(got, refs)
+    assert worst <= 1e-4 * max(float(np.abs(r).max()) for r in refs.values()), where
+    engine.cache.check()
+
+
+def test_command_line_generates_from_a_folder(tmp_path):
+    cfg = MODEL_Q
+    w = make_folder(str(tmp_path), cfg, seed=15, dtype=torch.bfloat16)
+    run = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llmx"), "generate", str(tmp_path), "5,17,3,99", "-n", "6", "--temp", "0",
+                          "--ignore-eos", "--dtype", "f32"], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    ids = next(l for l in run.stdout.splitlines() if l.startswith("ids: "))
+    tokens = [int(t) for t in ids[5:].split(",")]
+    assert len(tokens) == 6
+    seq = [5, 17, 3, 99]
+    for t in tokens:
+        logits = plain.forward(cfg, w, seq)[-1]
+        best = int(np.argmax(logits))
+        assert t == best or logits[best] - logits[t] <= 1e-4 * np.abs(logits).max()
+        seq.append(t)
+
+
+def test_trace_run_program(tmp_path):
+    cfg = MODEL_Q
+    w = make_folder(str(tmp_path / "m"), cfg, seed=12, dtype=torch.bfloat16, open_ranks=True)
+    requests = {f"q{i}": helpers.random_ids(cfg["vocab"], n, seed=50 + i) for i, n in enumerate([45, 3, 80, 20, 64])}
+    steps = helpers.trace_mixed(requests, tail=5)
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", BF16_BUDGET["Q"])):
+        out = tmp_path / ("out_" + dtype)
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(tmp_path / "m"), "--dtype", dtype,
+                               "--out", str(out), "--max-tokens", str(helpers.tokens_needed(steps))],
+                              input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        got = helpers.read_trace_output(steps, str(out), cfg["vocab"])
+        refs = {rid: plain.forward(cfg, w, ids) for rid, ids in requests.items()}
+        worst, where = worst_error(got, refs)
+        assert worst <= tol * max(float(np.abs(r).max()) for r in refs.values()), (dtype, worst, where)

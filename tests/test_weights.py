@@ -168,3 +168,27 @@ def test_random_values_are_a_function_of_seed_name_and_index():
     assert torch.equal(one.tensor("b.weight"), other.tensor("b.weight"))
     assert abs(float(one.tensor("b.weight").mean()) - 1.0) < 0.02
     assert not torch.equal(one.tensor("a.weight"), RandomSource(specs, 4, dtype=torch.float32).tensor("a.weight"))
+
+
+def test_data_off_its_element_size_is_read_all_the_same(tmp_path):
+    """An integer table after an odd number of 16-bit values, behind a header of odd length: the values are read as
+    they stand (copied out of the mapping), and what this package writes keeps every tensor on its element size."""
+    import json
+    import struct
+    from llmx_b200.weights.safetensors import SafetensorsFile, read_header
+    a = torch.tensor([1.5, -2.0, 0.25], dtype=torch.bfloat16)
+    b = torch.tensor([[7, -3], [100000, 2]], dtype=torch.int32)
+    header = json.dumps({"a": {"dtype": "BF16", "shape": [3], "data_offsets": [0, 6]},
+                         "b": {"dtype": "I32", "shape": [2, 2], "data_offsets": [6, 22]}}, separators=(",", ":")).encode()
+    if len(header) % 2 == 0:
+        header += b" "
+    path = str(tmp_path / "odd.safetensors")
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(header)) + header + a.view(torch.uint8).numpy().tobytes() + b.view(torch.uint8).numpy().tobytes())
+    f = SafetensorsFile(path)
+    assert torch.equal(f.tensor("a"), a) and torch.equal(f.tensor("b"), b)
+    f.close()
+    path = str(tmp_path / "own.safetensors")
+    write_safetensors(path, {"a": a, "b": b, "c": torch.tensor([3.0])})
+    entries, _ = read_header(path)
+    assert entries["b"].begin < entries["a"].begin and all((e.begin - entries["b"].begin) % 2 == 0 for e in entries.values())

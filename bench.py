@@ -125,7 +125,9 @@ def reference_arm(args):
 
 
 # Layer sizes for `--design buzetar`: a Buzetar of `layers` layers (its three mixers in turn) beside a dense Qwen3 of the
-# same width, depth, feed-forward width and head count.
+# same width, depth, feed-forward width and head count.  `--design kisepel`: a Kisepel of as many layers (its three mixers
+# in turn; 16 experts of a quarter of the feed-forward width, two a token, beside a shared one of half the width, so that a
+# token meets as many feed-forward weights as in the dense models) beside the Buzetar of the same sizes.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=6144, vocab=32768, q_rank=768, kv_rank=512, rot=64, window=2048, layers=6),
     "w4096": dict(width=4096, heads=32, ff=12288, vocab=32768, q_rank=1536, kv_rank=512, rot=64, window=4096, layers=3),
@@ -134,18 +136,19 @@ DESIGN_SIZES = {
 
 def design_bench(args) -> int:
     """`--design buzetar`: a 2,048-token prompt and decode steps of --batch requests after --context tokens, for Buzetar
-    and for a Qwen3 of equal size, bfloat16, random weights, with the device time by kernel of one plain step of each."""
+    and for a Qwen3 of equal size, bfloat16, random weights, with the device time by kernel of one plain step of each.
+    `--design kisepel`: the same for Kisepel and for a Buzetar of equal size."""
     import statistics
     import torch
     from llmx_b200 import ops
-    from llmx_b200.config import BuzetarConfig, Qwen3Config
+    from llmx_b200.config import BuzetarConfig, KisepelConfig, Qwen3Config
     from llmx_b200.engine import Engine, EngineOptions, StepEntry
     from llmx_b200.engine.decode_loop import DecodeSession
     torch.cuda.set_device(0)
     host_gen = torch.Generator()
     host_gen.manual_seed(2)
     page, T, B, C = 16, args.prefill_tokens, args.batch, args.context
-    out = {"design": "buzetar", "dtype": "bf16", "data": "synthetic", "prefill_tokens": T, "batch": B, "context": C,
+    out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prefill_tokens": T, "batch": B, "context": C,
            "steps": args.steps, "warmup": args.warmup, "sizes": {}}
     for name in (args.design_size.split(",") if args.design_size else sorted(DESIGN_SIZES)):
         z = DESIGN_SIZES[name]
@@ -160,8 +163,19 @@ def design_bench(args) -> int:
                                        "logit_scale": 1.0, "layers": [kinds[i % 3] for i in range(L)]})
         qwen = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=L, hidden_size=E, intermediate_size=F, num_attention_heads=H,
                                           num_key_value_heads=max(H // 4, 1), vocab_size=z["vocab"]))
+        decays = [1.0 - 2.0 ** -(3 + 5 * h / H) for h in range(H)]
+        experts = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": F // 4}, "shared": {"ff": F // 2}}
+        kis_kinds = [
+            {"type": "mamba2", "mixer": {"heads": H, "vdim": 128, "state": 128, "groups": max(H // 4, 1), "conv": 4, "norm_groups": max(H // 4, 1)}, "mlp": experts},
+            {"type": "parallel", "mixer": {
+                "left": {"heads": H, "kv_heads": max(H // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 4 * z["window"]},
+                         "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0}}},
+                "right": {"heads": H, "kv_heads": H // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": E // 16, "gate_rank": E // 16}}, "mlp": experts},
+            {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": decays}, "mlp": experts}]
+        kis = KisepelConfig.from_dict({"architecture": "Kisepel", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                                       "logit_scale": 1.0, "layers": [kis_kinds[i % 3] for i in range(L)]})
         res = {}
-        for tag, cfg in (("buzetar", buz), ("qwen3", qwen)):
+        for tag, cfg in ((("kisepel", kis), ("buzetar", buz)) if args.design == "kisepel" else (("buzetar", buz), ("qwen3", qwen))):
             per_request = -(-(C + 3 * args.steps + args.warmup + 64) // page) * page
             engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=max(B * per_request, T + page),
                                                                            page_size=page, max_requests=B, record_after=2))
@@ -235,9 +249,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill", "sample"], default=None,
                     help="run one part only (for profiling); the line then holds only that part")
-    ap.add_argument("--design", choices=["buzetar"], default=None,
+    ap.add_argument("--design", choices=["buzetar", "kisepel"], default=None,
                     help="instead of the default workload: prompt and decode throughput of this design at sizes that resemble a "
-                         "real model's layers, beside a Qwen3 of equal size (one JSON line of its own)")
+                         "real model's layers, beside the closest other design of equal size (Buzetar beside Qwen3, Kisepel beside Buzetar; one JSON line of its own)")
     ap.add_argument("--design-size", default=None, help="with --design: one of " + ", ".join(sorted(DESIGN_SIZES)) + " (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":

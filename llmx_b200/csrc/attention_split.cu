@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, QT* __restrict__ out,
                        const int* __restrict__ row_request, const int* __restrict__ positions,
                        const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int D, int V,
-                       int page_size, int window, int chunk, float scale) {
+                       int page_size, int window, int chunk, float scale, int splits, float* __restrict__ partial) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];  // WARPS * (V + 2)
@@ -108,7 +108,15 @@ attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    for (int t = lo + warp; t <= pos; t += WARPS) {
+    // With `splits` > 1 the row's keys are cut into that many equal ranges, one a block (blockIdx.z); each leaves its
+    // partial state (sum, maximum, weight) and a second kernel merges them in range order.
+    int first = lo, last = pos;
+    if (splits > 1) {
+        const int per = (pos - lo + splits) / splits;
+        first = lo + (int)blockIdx.z * per;
+        last = min(pos, first + per - 1);
+    }
+    for (int t = first + warp; t <= last; t += WARPS) {
         const int page = table[t / page_size], off = t % page_size;
         const KVT* kp = cache + (((size_t)page * kv_heads + g) * page_size + off) * (size_t)W;
         const KVT* vp = kp + D;
@@ -151,12 +159,258 @@ attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
             f[w] = mw == -INFINITY ? 0.0f : expf(mw - mm);
             ll += smem[w * (V + 2) + V + 1] * f[w];
         }
+        if (splits > 1) {
+            float* prow = partial + (((size_t)row * heads + h) * splits + blockIdx.z) * (size_t)(V + 2);
+            for (int d = lane; d < V; d += 32) {
+                float o = 0.0f;
+                for (int w = 0; w < WARPS; ++w) o += smem[w * (V + 2) + d] * f[w];
+                prow[d] = o;
+            }
+            if (lane == 0) {
+                prow[V] = mm;
+                prow[V + 1] = ll;
+            }
+            return;
+        }
         QT* orow = out + ((size_t)row * heads + h) * V;
         for (int d = lane; d < V; d += 32) {
             float o = 0.0f;
             for (int w = 0; w < WARPS; ++w) o += smem[w * (V + 2) + d] * f[w];
             orow[d] = from_float<QT>(o / ll);
         }
+    }
+}
+
+// The ranges' partial states of one (row, head), merged in range order.  One warp a (row, head).
+template <typename QT>
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const float* __restrict__ partial, QT* __restrict__ out, int items, int V, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const float* p = partial + (size_t)item * splits * (V + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[(size_t)s * (V + 2) + V]);
+    float ll = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = p[(size_t)s * (V + 2) + V];
+        ll += ms == -INFINITY ? 0.0f : p[(size_t)s * (V + 2) + V + 1] * expf(ms - mm);
+    }
+    for (int d = lane; d < V; d += 32) {
+        float o = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[(size_t)s * (V + 2) + V];
+            if (ms != -INFINITY) o += p[(size_t)s * (V + 2) + d] * expf(ms - mm);
+        }
+        out[(size_t)item * V + d] = from_float<QT>(o / ll);
+    }
+}
+
+// ---- the tiled form, on the tensor cores ----------------------------------------------------------------------------
+// bfloat16 queries and cache, D and V multiples of 16.  A block of four warps takes 64 rows that share their keys: TOK
+// tokens in a row of one request times the R_PAD heads (the group's head count rounded up to a power of two) of one
+// key/value head; warp w owns rows 16 w .. 16 w + 15 for all keys (mma.sync m16n8k16, 32-bit sums).  Keys come in tiles
+// of 64, whole [key ; value] rows copied from their pages by cp.async into two buffers, the next tile in flight while
+// this one is multiplied.  Scores and the online softmax are 32-bit; a weight enters the second product as the sum
+// of three bfloat16 values, each the rounding of what the ones before left over, so that the weights keep their 32-bit
+// value (three products instead of one; their sums are 32-bit).  Values are read as the B operand through
+// ldmatrix.trans.  A block finds its tile from its index by walking the requests' row counts, so nothing is planned on
+// the host and a recorded step holds for any histories.
+constexpr int TL_ROWS = 64, TL_KEYS = 64, TL_PAD = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Three bfloat16 values whose sum is x to 24 bits, for two neighbouring weights at once.
+__device__ __forceinline__ void split3(float x, float y, uint32_t& a, uint32_t& b, uint32_t& c) {
+    const __nv_bfloat16 x0 = __float2bfloat16_rn(x), y0 = __float2bfloat16_rn(y);
+    const float xr = x - __bfloat162float(x0), yr = y - __bfloat162float(y0);
+    const __nv_bfloat16 x1 = __float2bfloat16_rn(xr), y1 = __float2bfloat16_rn(yr);
+    const __nv_bfloat16 x2 = __float2bfloat16_rn(xr - __bfloat162float(x1)), y2 = __float2bfloat16_rn(yr - __bfloat162float(y1));
+    __nv_bfloat162 p0(x0, y0), p1(x1, y1), p2(x2, y2);
+    a = *reinterpret_cast<uint32_t*>(&p0);
+    b = *reinterpret_cast<uint32_t*>(&p1);
+    c = *reinterpret_cast<uint32_t*>(&p2);
+}
+
+template <int VN_MAX>
+__global__ void __launch_bounds__(128)
+attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ row_start, const int* __restrict__ row_count,
+                       const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int requests,
+                       int heads, int kv_heads, int D, int V, int page_size, int window, int chunk, float scale, int r_pad) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char tl_smem[];
+    const int ratio = heads / kv_heads, tok = TL_ROWS / r_pad;
+    // Which tile: the requests' tiles are numbered one request after the other.
+    int idx = blockIdx.x, r = 0, tiles_r = 0;
+    for (; r < requests; ++r) {
+        tiles_r = (row_count[r] + tok - 1) / tok;
+        if (idx < tiles_r) break;
+        idx -= tiles_r;
+    }
+    if (r >= requests) return;
+    const int g = blockIdx.y;
+    const int t0 = idx * tok, n_rows = row_count[r], a0 = row_start[r], hist = history[r];
+    const int n_tok = min(tok, n_rows - t0);
+    const int W = D + V, qs = D + TL_PAD, ws = W + TL_PAD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tl_smem);
+    __nv_bfloat16* KV = Qs + (size_t)TL_ROWS * qs;               // [2][TL_KEYS][ws]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    auto lowest = [&](int p) {
+        int lo = window > 0 ? max(0, p - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+        return lo;
+    };
+    const int p_first = hist + t0, p_last = hist + t0 + n_tok - 1;
+    const int key0 = lowest(p_first);
+    const int n_tiles = (p_last - key0 + TL_KEYS) / TL_KEYS;
+    const int* table = block_tables + (size_t)r * table_stride;
+    const int w8 = W / 8;
+    auto issue = [&](int tile, int which) {
+        __nv_bfloat16* buf = KV + (size_t)which * TL_KEYS * ws;
+        const int kt0 = key0 + tile * TL_KEYS;
+        for (int i = threadIdx.x; i < TL_KEYS * w8; i += 128) {
+            const int j = i / w8, c = i - j * w8;
+            const int t = kt0 + j;
+            __nv_bfloat16* dst = buf + (size_t)j * ws + 8 * c;
+            if (t <= p_last) {
+                const int page = table[t / page_size];
+                const __nv_bfloat16* src = cache + (((size_t)page * kv_heads + g) * page_size + t % page_size) * (size_t)W + 8 * c;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);      // no key here: a zero weight must meet a finite value
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue(0, 0);
+    // The tile's queries: row i is token t0 + i / r_pad, head g * ratio + i % r_pad (rows past the heads or the tokens are zeros).
+    const int d8 = D / 8;
+    for (int i = threadIdx.x; i < TL_ROWS * d8; i += 128) {
+        const int row = i / d8, c = i - row * d8;
+        const int tk = row / r_pad, hd = row % r_pad;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tk < n_tok && hd < ratio)
+            v = *reinterpret_cast<const uint4*>(q + ((size_t)(a0 + t0 + tk) * heads + (size_t)g * ratio + hd) * D + 8 * c);
+        *reinterpret_cast<uint4*>(Qs + (size_t)row * qs + 8 * c) = v;
+    }
+    bool valid[2];
+    int pos[2], lo[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const int row = 16 * warp + gid + 8 * hf;
+        const int tk = row / r_pad, hd = row % r_pad;
+        valid[hf] = tk < n_tok && hd < ratio;
+        pos[hf] = hist + t0 + tk;
+        lo[hf] = lowest(pos[hf]);
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[VN_MAX][4];
+#pragma unroll
+    for (int i = 0; i < VN_MAX; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const int vn = V / 8;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                 // this tile has landed (and the queries); everyone has left the other buffer
+        if (tile + 1 < n_tiles) issue(tile + 1, (tile + 1) & 1);
+        const __nv_bfloat16* buf = KV + (size_t)(tile & 1) * TL_KEYS * ws;
+        const int kt0 = key0 + tile * TL_KEYS;
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+        for (int kk = 0; kk < D; kk += 16) {
+            uint32_t a[4];
+            const __nv_bfloat16* qa = Qs + (size_t)(16 * warp + gid) * qs + kk + 2 * tig;
+            a[0] = *reinterpret_cast<const uint32_t*>(qa);
+            a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * qs);
+            a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * qs + 8);
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const __nv_bfloat16* kb = buf + (size_t)(8 * n + gid) * ws + kk + 2 * tig;
+                mma_bf16_16816(s[n], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int hf = i >> 1, key = kt0 + 8 * n + 2 * tig + (i & 1);
+                const bool seen = valid[hf] && key >= lo[hf] && key <= pos[hf];
+                s[n][i] = seen ? s[n][i] * scale : -INFINITY;
+                mx[hf] = fmaxf(mx[hf], s[n][i]);
+            }
+        float corr[2], base[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+            mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+            const float m_new = fmaxf(m[hf], mx[hf]);
+            base[hf] = m_new == -INFINITY ? 0.0f : m_new;
+            corr[hf] = expf(m[hf] - base[hf]);           // exp(-inf) = 0 before the row's first key
+            m[hf] = m_new;
+            l[hf] *= corr[hf];
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s[n][i] = expf(s[n][i] - base[i >> 1]);
+                l[i >> 1] += s[n][i];
+            }
+#pragma unroll
+        for (int nv = 0; nv < VN_MAX; ++nv) {
+            o[nv][0] *= corr[0];
+            o[nv][1] *= corr[0];
+            o[nv][2] *= corr[1];
+            o[nv][3] *= corr[1];
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t p0[4], p1[4], p2[4];
+            split3(s[2 * ks][0], s[2 * ks][1], p0[0], p1[0], p2[0]);
+            split3(s[2 * ks][2], s[2 * ks][3], p0[1], p1[1], p2[1]);
+            split3(s[2 * ks + 1][0], s[2 * ks + 1][1], p0[2], p1[2], p2[2]);
+            split3(s[2 * ks + 1][2], s[2 * ks + 1][3], p0[3], p1[3], p2[3]);
+            const __nv_bfloat16* vrow = buf + (size_t)(16 * ks + (lane & 15)) * ws + D;
+#pragma unroll
+            for (int nv = 0; nv < VN_MAX; ++nv) {
+                if (nv < vn) {
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                                 : "=r"(b0), "=r"(b1) : "r"((uint32_t)__cvta_generic_to_shared(vrow + 8 * nv)));
+                    mma_bf16_16816(o[nv], p2, b0, b1);   // the smallest parts first
+                    mma_bf16_16816(o[nv], p1, b0, b1);
+                    mma_bf16_16816(o[nv], p0, b0, b1);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        l[hf] += __shfl_xor_sync(0xffffffffu, l[hf], 1);
+        l[hf] += __shfl_xor_sync(0xffffffffu, l[hf], 2);
+        if (!valid[hf]) continue;
+        const int row = 16 * warp + gid + 8 * hf;
+        const int tk = row / r_pad, hd = row % r_pad;
+        const float inv = 1.0f / l[hf];
+        __nv_bfloat16* orow = out + ((size_t)(a0 + t0 + tk) * heads + (size_t)g * ratio + hd) * V;
+#pragma unroll
+        for (int nv = 0; nv < VN_MAX; ++nv)
+            if (nv < vn)
+                *reinterpret_cast<uint32_t*>(orow + 8 * nv + 2 * tig) = pack_bf16(o[nv][2 * hf] * inv, o[nv][2 * hf + 1] * inv);
     }
 }
 }  // namespace
@@ -185,25 +439,70 @@ LLMX_EXPORT int llmx_qk_norm_rope_write(const float* proj, int stride, const flo
     return launch_status();
 }
 
-// q [rows, heads, D] and out [rows, heads, V] of `q_dtype`; the cache as above, of `cache_dtype`.
+// q [rows, heads, D] and out [rows, heads, V] of `q_dtype`; the cache as above, of `cache_dtype`.  `splits` > 1: a row's
+// keys are cut into that many ranges (a matter of speed only: steps of few rows over long histories), which meet in
+// `partial`, float32 [rows, heads, splits, V + 2].
 LLMX_EXPORT int llmx_attention_split(const void* q, int q_dtype, const void* cache, int cache_dtype, void* out,
                                      const int* row_request, const int* positions, const int* block_tables,
                                      int table_stride, int rows, int heads, int kv_heads, int D, int V, int page_size,
-                                     int window, int chunk, float scale, cudaStream_t stream) {
+                                     int window, int chunk, float scale, int splits, float* partial, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (D <= 0 || V <= 0 || D > 32 * MAX_PER_LANE || V > 32 * MAX_PER_LANE || heads % kv_heads || heads > 65535)
         return LLMX_ERR_UNSUPPORTED;
-    dim3 grid(rows, heads);
+    if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
+    dim3 grid(rows, heads, splits);
     const size_t shmem = (size_t)WARPS * (V + 2) * sizeof(float);
 #define LLMX_SPLIT(QT, KVT)                                                                                            \
     launch_kernel(attention_split_kernel<QT, KVT>, dim3(grid), dim3(WARPS * 32), shmem, stream, (const QT*)q,         \
                   (const KVT*)cache, (QT*)out, row_request, positions, block_tables, table_stride, heads, kv_heads, D, \
-                  V, page_size, window, chunk, scale)
+                  V, page_size, window, chunk, scale, splits, partial)
     if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) LLMX_SPLIT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) LLMX_SPLIT(__nv_bfloat16, float);
     else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) LLMX_SPLIT(float, __nv_bfloat16);
     else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_F32) LLMX_SPLIT(float, float);
     else return LLMX_ERR_UNSUPPORTED;
 #undef LLMX_SPLIT
+    int status = launch_status();
+    if (status || splits == 1) return status;
+    const int items = rows * heads;
+    if (q_dtype == LLMX_BF16)
+        launch_kernel(attention_merge_kernel<__nv_bfloat16>, dim3((items + 3) / 4), dim3(128), 0, stream, (const float*)partial, (__nv_bfloat16*)out, items, V, splits);
+    else
+        launch_kernel(attention_merge_kernel<float>, dim3((items + 3) / 4), dim3(128), 0, stream, (const float*)partial, (float*)out, items, V, splits);
     return launch_status();
+}
+
+// Whether the tiled form takes these sizes (bfloat16 queries and cache are the caller's to check).
+LLMX_EXPORT int llmx_attention_tiled_fits(int heads, int kv_heads, int D, int V) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > TL_ROWS) return 0;
+    if (D <= 0 || V <= 0 || D % 16 || V % 16 || D > 256 || V > 256) return 0;
+    const size_t smem = ((size_t)TL_ROWS * (D + TL_PAD) + 2 * (size_t)TL_KEYS * (D + V + TL_PAD)) * 2;
+    return smem <= 200 * 1024;
+}
+
+// The tiled form: q [rows, heads, D], out [rows, heads, V] and the cache bfloat16; the step's row ranges and histories
+// on the device; `rows`: the step's rows (for the grid's size only).
+LLMX_EXPORT int llmx_attention_tiled(const void* q, const void* cache, void* out, const int* row_start, const int* row_count,
+                                     const int* history, const int* block_tables, int table_stride, int rows, int requests,
+                                     int heads, int kv_heads, int D, int V, int page_size, int window, int chunk, float scale,
+                                     cudaStream_t stream) {
+    if (rows <= 0 || requests <= 0) return 0;
+    if (!llmx_attention_tiled_fits(heads, kv_heads, D, V) || kv_heads > 65535) return LLMX_ERR_UNSUPPORTED;
+    int r_pad = 1;
+    while (r_pad < heads / kv_heads) r_pad *= 2;
+    const int tok = TL_ROWS / r_pad;
+    dim3 grid((rows + tok - 1) / tok + requests, kv_heads);
+    const size_t smem = ((size_t)TL_ROWS * (D + TL_PAD) + 2 * (size_t)TL_KEYS * (D + V + TL_PAD)) * 2;
+#define LLMX_TILED(VN)                                                                                                   \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_tiled_kernel<VN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_kernel(attention_tiled_kernel<VN>, dim3(grid), dim3(128), smem, stream, (const __nv_bfloat16*)q,          \
+                      (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, row_start, row_count, history, block_tables,    \
+                      table_stride, requests, heads, kv_heads, D, V, page_size, window, chunk, scale, r_pad);           \
+        return launch_status();                                                                                           \
+    } while (0)
+    if (V <= 64) LLMX_TILED(8);
+    if (V <= 128) LLMX_TILED(16);
+    LLMX_TILED(32);
+#undef LLMX_TILED
 }

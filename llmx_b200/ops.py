@@ -107,7 +107,9 @@ _SIGNATURES = {
     ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _i, _i, _f,
                                           _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
     ("attention_split", "llmx_qk_norm_rope_write"): [_p, _i, _p, _p, _f, _p, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p],
-    ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+    ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
+    ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
     ("moe", "llmx_moe_route"): [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p],
     ("moe", "llmx_moe_product"): [_p, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_combine"): [_p, _p, _i, _i, _i, _f, _p],
@@ -525,10 +527,11 @@ def qk_norm_rope_write(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: i
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
                     positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int, window: Optional[int], chunk: Optional[int], scale: float) -> torch.Tensor:
+                    value_dim: int, window: Optional[int], chunk: Optional[int], scale: float, splits: int = 1) -> torch.Tensor:
     """Paged softmax attention, one block per (row, head); q [rows, heads * D] and out [rows, heads * V] of one type;
     cache [pages, 1, kv_heads, page, D + V].  A row at position p reads keys max(p - window + 1, floor(p / chunk) * chunk,
-    0) .. p."""
+    0) .. p.  `splits` > 1: a row's keys are cut into that many ranges, a block each, merged by a second kernel in
+    range order (for steps of few rows over long histories; the result is the same up to the order of sums)."""
     _cuda(q, cache, out, row_request, positions, block_tables)
     rows = q.shape[0]
     _need(q.shape[1] == heads * key_dim and tuple(out.shape) == (rows, heads * value_dim) and q.dtype == out.dtype,
@@ -538,10 +541,37 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row
     for t in (row_request, positions, block_tables):
         _need(t.dtype == torch.int32, "attention: metadata must be int32")
     _need(block_tables.dim() == 2 and row_request.numel() >= rows and positions.numel() >= rows, "attention: metadata shapes do not fit")
+    splits = max(1, min(int(splits), 64))
+    partial = torch.empty((rows, heads, splits, value_dim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(_fn("attention_split", "llmx_attention_split")(
         _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
         block_tables.shape[1], rows, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0), int(chunk or 0),
-        float(scale), _stream()), "attention_split")
+        float(scale), splits, _ptr(partial), _stream()), "attention_split", 2 if splits > 1 else 1)
+    return out
+
+
+def attention_tiled_fits(heads: int, kv_heads: int, key_dim: int, value_dim: int) -> bool:
+    """Whether the tiled form of `attention_split` takes these sizes (it also wants bfloat16 queries and cache)."""
+    f = _fn("attention_split", "llmx_attention_tiled_fits")
+    return bool(f(int(heads), int(kv_heads), int(key_dim), int(value_dim)))
+
+
+def attention_tiled(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, block_tables: torch.Tensor, heads: int,
+                    kv_heads: int, key_dim: int, value_dim: int, window: Optional[int], chunk: Optional[int], scale: float) -> torch.Tensor:
+    """`attention_split` on the tensor cores (csrc/attention_split.cu): bfloat16 q [rows, heads * D], out [rows, heads * V]
+    and cache; 64 rows that share their keys a block, keys in tiles of 64; softmax weights enter the second product
+    as sums of three bfloat16 values.  `step`: the StepBatch (row ranges and histories are read on the device)."""
+    _cuda(q, cache, out, block_tables)
+    rows = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16, "attention_tiled: bfloat16 queries, output and cache")
+    _need(q.shape[1] == heads * key_dim and tuple(out.shape) == (rows, heads * value_dim), "attention: q and out shapes do not fit")
+    _need(cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == kv_heads and cache.shape[4] == key_dim + value_dim,
+          "attention: cache layout does not fit")
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and rows == step.rows, "attention: metadata does not fit")
+    _check(_fn("attention_split", "llmx_attention_tiled")(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(block_tables),
+        block_tables.shape[1], rows, step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0),
+        int(chunk or 0), float(scale), _stream()), "attention_tiled")
     return out
 
 

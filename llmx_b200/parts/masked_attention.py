@@ -81,6 +81,8 @@ class MaskedAttention(Part):
             self.q_norm = tensors[qn].to(torch.float32).contiguous()
             self.k_norm = tensors[kn].to(torch.float32).contiguous()
         self.freq = torch.from_numpy(self.frequencies()).to(self.o.weight.device) if self.rot_dims else None
+        self.tiled = precision.act is torch.bfloat16 and not precision.invariant and \
+            ops.attention_tiled_fits(self.heads, self.kv_heads, self.key_dim, self.value_dim)
 
     def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
                 write_cache: bool = True) -> None:
@@ -95,6 +97,16 @@ class MaskedAttention(Part):
         ops.qk_norm_rope_write(proj, self.heads, self.kv_heads, self.key_dim, self.value_dim, self.q_norm, self.k_norm,
                                float(self.qk_norm_eps or 0.0), self.freq, step.positions, slots, q, cache)
         o = torch.empty((rows, self.o_width), dtype=self.precision.act, device=h.device)
-        ops.attention_split(q, cache, o, step.row_request, step.positions, group.block_tables, self.heads, self.kv_heads,
-                            self.key_dim, self.value_dim, self.window, self.chunk, self.scale)
+        # Which kernel is a matter of speed only.  Steps that bring some request more than a few rows run the tiled
+        # form (bfloat16, sizes it takes); others run the plain form, a row's keys cut into ranges when the rows alone
+        # would not fill the device.
+        if self.tiled and step.max_row_count > 4 and cache.dtype is torch.bfloat16:
+            ops.attention_tiled(q, cache, o, step, group.block_tables, self.heads, self.kv_heads, self.key_dim, self.value_dim,
+                                self.window, self.chunk, self.scale)
+        else:
+            span = min(x for x in (step.max_context, self.window, self.chunk) if x)
+            blocks = rows * self.heads
+            splits = 1 if self.precision.invariant else max(1, min(32, span // 128, 2368 // max(blocks, 1)))
+            ops.attention_split(q, cache, o, step.row_request, step.positions, group.block_tables, self.heads, self.kv_heads,
+                                self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits)
         self.o(o, out=residual, accumulate=True)

@@ -110,7 +110,8 @@ _SIGNATURES = {
     ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
     ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
-    ("moe", "llmx_moe_route"): [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p],
+    ("moe", "llmx_moe_route"): [_p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p],
+    ("moe", "llmx_moe_product_few"): [_p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_product"): [_p, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_combine"): [_p, _p, _i, _i, _i, _f, _p],
     ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
@@ -576,28 +577,62 @@ def attention_tiled(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ste
 
 
 def moe_tiles_len(pairs: int, experts: int) -> int:
+    """Ints the tiles of a routing take at most (tiles of 32 pairs; tiles of 128 are fewer)."""
     return 2 + 2 * ((pairs + 31) // 32 + experts)
 
 
+_moe_tile_rows = {}
+
+
+def moe_tensor_cores_fit(dtype: torch.dtype, *inner_widths: int) -> bool:
+    """Whether the experts' products of this type over these inner widths can all run the tensor-core form."""
+    f = getattr(_build.load("moe"), "llmx_moe_tensor_cores_fit")
+    f.argtypes, f.restype = [_i, _i], _i
+    return dtype in _CODE and all(bool(f(_CODE[dtype], int(k))) for k in inner_widths)
+
+
+def moe_product_few(a: torch.Tensor, a_div: int, w: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, pairs: int,
+                    out: torch.Tensor, gated: bool) -> torch.Tensor:
+    """`moe_product` for steps of a few pairs (bfloat16, inner width a multiple of 8): a block a pair and 16 output
+    columns, the pair's expert read from the table, no lists."""
+    _cuda(a, w, token_ids, table, out)
+    experts, wn, K = w.shape
+    N = wn // 2 if gated else wn
+    vocab, top = table.shape
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and a.shape[1] == K and a.shape[0] * a_div >= pairs,
+          "moe_product_few: bfloat16 rows that fit the weights")
+    _need(token_ids.dtype == torch.int32 and table.dtype == torch.int32 and token_ids.numel() * top >= pairs, "moe_product_few: int32 ids and table")
+    _need(tuple(out.shape) == (pairs, N), "moe_product_few: output shape does not fit")
+    _check(_fn("moe", "llmx_moe_product_few")(_ptr(a), int(a_div), _ptr(w), _ptr(token_ids), _ptr(table), top, vocab, pairs, experts,
+                                              _ptr(out), _code(out), N, K, 1 if gated else 0, _stream()), "moe_product_few")
+    return out
+
+
 def moe_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, lists: torch.Tensor, counts: torch.Tensor,
-              tiles: torch.Tensor) -> None:
+              tiles: torch.Tensor, tensor_cores: bool = False) -> None:
     """Sort the step's (row, k) pairs by the expert the table gives them: lists int32 [experts, rows * top] (pairs in
-    order), counts int32 [experts], tiles int32 [moe_tiles_len] (their number, then (expert, first place) of every tile
-    of 32 pairs)."""
+    order), counts int32 [experts], tiles int32 [moe_tiles_len] (their number, their size, then (expert, first place) of
+    every tile).  `tensor_cores`: the form of `moe_product` that will run (it sets the tiles' size: 128 pairs, else 32)."""
     _cuda(token_ids, table, lists, counts, tiles)
     rows, (vocab, top) = token_ids.numel(), table.shape
     for t in (token_ids, table, lists, counts, tiles):
         _need(t.dtype == torch.int32, "moe_route: int32 tensors")
     _need(lists.numel() >= experts * rows * top and counts.numel() >= experts and tiles.numel() >= moe_tiles_len(rows * top, experts),
           "moe_route: outputs too small")
+    tile_rows = _moe_tile_rows.get(bool(tensor_cores))
+    if tile_rows is None:
+        f = getattr(_build.load("moe"), "llmx_moe_tile_rows")
+        f.argtypes, f.restype = [_i], _i
+        tile_rows = _moe_tile_rows[bool(tensor_cores)] = f(1 if tensor_cores else 0)
     _check(_fn("moe", "llmx_moe_route")(_ptr(token_ids), _ptr(table), top, rows, experts, vocab, _ptr(lists), _ptr(counts),
-                                        _ptr(tiles), _stream()), "moe_route", 2)
+                                        _ptr(tiles), tile_rows, _stream()), "moe_route", 2)
 
 
 def moe_product(a: torch.Tensor, a_div: int, w: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor, tiles: torch.Tensor,
-                pairs: int, out: torch.Tensor, gated: bool, tensor_cores: bool = True) -> torch.Tensor:
+                pairs: int, out: torch.Tensor, gated: bool, tensor_cores: bool = False) -> torch.Tensor:
     """out[pair] = a[pair // a_div] W_e^T for the expert e whose list holds the pair; w [experts, N (gated: 2 N, gate rows
-    then up rows), K] of a's type.  gated: out = silu(gate) * up in out's type; else float32."""
+    then up rows), K] of a's type.  gated: out = silu(gate) * up in out's type; else float32.  `tensor_cores` as the
+    routing was told."""
     _cuda(a, w, lists, counts, tiles, out)
     experts, wn, K = w.shape
     N = wn // 2 if gated else wn

@@ -114,6 +114,8 @@ class TableRoutedExperts(Part):
     by expert on the device and the products run a tile of one expert's pairs at a time (csrc/moe.cu), so nothing of
     the routing is read on the host.  Tensor roles: `table`, `e<i>.gate|up|down`; the shared part's under `shared.`."""
 
+    few_pairs = 64          # up to this many (row, expert) pairs a step, the products run the form for a few pairs
+
     def __init__(self, hidden: int, vocab: int, experts: int, top: int, intermediate: int, shared: Optional[Part] = None,
                  names=("gate", "up", "down"), table_role: str = "table", shared_name: str = "shared"):
         if not 1 <= top <= experts:
@@ -143,6 +145,8 @@ class TableRoutedExperts(Part):
         act = precision.act
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.{g}"], tensors[f"e{e}.{u}"]], dim=0) for e in range(self.experts)]).to(act).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.{d}"] for e in range(self.experts)]).to(act).contiguous()
+        from .. import ops
+        self.tensor_cores = not precision.invariant and ops.moe_tensor_cores_fit(act, self.hidden, self.intermediate)
 
     def forward(self, h: torch.Tensor, step: StepBatch, residual: torch.Tensor) -> None:
         from .. import ops
@@ -152,15 +156,20 @@ class TableRoutedExperts(Part):
             raise runtime.KernelError("experts: rows of the path's type and the part's width, a float32 residual")
         pairs = rows * self.top
         dev = h.device
-        lists = torch.empty((self.experts, pairs), dtype=torch.int32, device=dev)
-        counts = torch.empty((self.experts,), dtype=torch.int32, device=dev)
-        tiles = torch.empty((ops.moe_tiles_len(pairs, self.experts),), dtype=torch.int32, device=dev)
-        ops.moe_route(step.token_ids, self.table, self.experts, lists, counts, tiles)
-        tc = not self.precision.invariant
         act = torch.empty((pairs, self.intermediate), dtype=self.precision.act, device=dev)
-        ops.moe_product(h, self.top, self.w_gate_up, lists, counts, tiles, pairs, act, gated=True, tensor_cores=tc)
         y = torch.empty((pairs, self.hidden), dtype=torch.float32, device=dev)
-        ops.moe_product(act, 1, self.w_down, lists, counts, tiles, pairs, y, gated=False, tensor_cores=tc)
+        if self.tensor_cores and pairs <= self.few_pairs:
+            # A few pairs (decoding): the experts' weights streamed once a pair; which form runs follows the step's rows alone.
+            ops.moe_product_few(h, self.top, self.w_gate_up, step.token_ids, self.table, pairs, act, gated=True)
+            ops.moe_product_few(act, 1, self.w_down, step.token_ids, self.table, pairs, y, gated=False)
+        else:
+            lists = torch.empty((self.experts, pairs), dtype=torch.int32, device=dev)
+            counts = torch.empty((self.experts,), dtype=torch.int32, device=dev)
+            tiles = torch.empty((ops.moe_tiles_len(pairs, self.experts),), dtype=torch.int32, device=dev)
+            tc = self.tensor_cores
+            ops.moe_route(step.token_ids, self.table, self.experts, lists, counts, tiles, tensor_cores=tc)
+            ops.moe_product(h, self.top, self.w_gate_up, lists, counts, tiles, pairs, act, gated=True, tensor_cores=tc)
+            ops.moe_product(act, 1, self.w_down, lists, counts, tiles, pairs, y, gated=False, tensor_cores=tc)
         ops.moe_combine_(residual, y, self.top, 1.0 / self.top)
         if self.shared is not None:
             self.shared.forward(h, step, residual)

@@ -203,7 +203,7 @@ def test_row_kernels_against_the_plain_functions():
     assert np.abs(norm.forward(xs.to(DEV)).cpu().numpy() - plain.rms_norm(xs.numpy(), wz.numpy(), 1e-6, one_plus=True)).max() <= 1e-5
 
 
-@pytest.mark.parametrize("rows,experts,top,K,N", [(1, 4, 2, 64, 40), (37, 5, 3, 96, 72), (300, 3, 1, 160, 136), (64, 8, 8, 32, 8)])
+@pytest.mark.parametrize("rows,experts,top,K,N", [(1, 4, 2, 64, 64), (37, 5, 3, 96, 96), (300, 3, 1, 160, 128), (64, 8, 8, 32, 32), (700, 2, 2, 256, 224)])
 def test_expert_products_on_the_tensor_cores_equal_those_on_the_cuda_cores(rows, experts, top, K, N):
     """The grouped products of the experts in bfloat16: tensor-core tiles against the CUDA-core kernel (the same
     bfloat16 inputs, 32-bit sums), and both against a plain loop over the pairs; tiles that are full, partial, and
@@ -221,19 +221,25 @@ def test_expert_products_on_the_tensor_cores_equal_those_on_the_cuda_cores(rows,
     lists = torch.empty((experts, pairs), dtype=torch.int32, device=DEV)
     counts = torch.empty((experts,), dtype=torch.int32, device=DEV)
     tiles = torch.empty((ops.moe_tiles_len(pairs, experts),), dtype=torch.int32, device=DEV)
-    ops.moe_route(ids.to(DEV), table.to(DEV), experts, lists, counts, tiles)
-    cnt = counts.cpu().numpy()
-    assert cnt.sum() == pairs and int(tiles[0]) == sum(-(-int(c) // 32) for c in cnt)
-    for e in range(experts):
-        mine = lists[e, :cnt[e]].cpu().numpy()
-        assert list(mine) == sorted(mine) and all(int(table[ids[p // top], p % top]) == e for p in mine)
     results = []
     for tc in (True, False):
+        ops.moe_route(ids.to(DEV), table.to(DEV), experts, lists, counts, tiles, tensor_cores=tc)
+        cnt = counts.cpu().numpy()
+        assert cnt.sum() == pairs and int(tiles[0]) == sum(-(-int(c) // (128 if tc else 32)) for c in cnt)
+        for e in range(experts):
+            mine = lists[e, :cnt[e]].cpu().numpy()
+            assert list(mine) == sorted(mine) and all(int(table[ids[p // top], p % top]) == e for p in mine)
         act = torch.full((pairs, N), 7.0, dtype=torch.bfloat16, device=DEV)
         ops.moe_product(h.to(DEV), top, w_gu.to(DEV), lists, counts, tiles, pairs, act, gated=True, tensor_cores=tc)
         y = torch.full((pairs, K), 7.0, dtype=torch.float32, device=DEV)
         ops.moe_product(act, 1, w_d.to(DEV), lists, counts, tiles, pairs, y, gated=False, tensor_cores=tc)
         results.append((act.float().cpu().numpy(), y.cpu().numpy()))
+    # The form for steps of a few pairs (no lists: the pair's expert comes from the table) makes the same two products.
+    act = torch.full((pairs, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.moe_product_few(h.to(DEV), top, w_gu.to(DEV), ids.to(DEV), table.to(DEV), pairs, act, gated=True)
+    y = torch.full((pairs, K), 7.0, dtype=torch.float32, device=DEV)
+    ops.moe_product_few(act, 1, w_d.to(DEV), ids.to(DEV), table.to(DEV), pairs, y, gated=False)
+    results.append((act.float().cpu().numpy(), y.cpu().numpy()))
     ref_act = np.zeros((pairs, N))
     for p in range(pairs):
         e = int(table[ids[p // top], p % top])
@@ -241,7 +247,8 @@ def test_expert_products_on_the_tensor_cores_equal_those_on_the_cuda_cores(rows,
         ref_act[p] = plain.silu(hp @ w_gu[e, :N].float().numpy().T.astype(np.float64)) * (hp @ w_gu[e, N:].float().numpy().T.astype(np.float64))
     for act, y in results:
         assert np.abs(act - ref_act).max() <= 2 ** -7 * max(1.0, np.abs(ref_act).max())
-    assert np.abs(results[0][1] - results[1][1]).max() <= 2e-2 * np.abs(results[1][1]).max()      # the two act matrices differ by roundings to bfloat16
+    for k in (0, 2):
+        assert np.abs(results[k][1] - results[1][1]).max() <= 2e-2 * np.abs(results[1][1]).max()  # the act matrices differ by roundings to bfloat16
     x = torch.zeros(rows, K, dtype=torch.float32, device=DEV)
     ops.moe_combine_(x, torch.from_numpy(results[1][1]).to(DEV), top, 1.0 / top)
     assert np.abs(x.cpu().numpy() - results[1][1].reshape(rows, top, K).sum(axis=1) / top).max() <= 1e-5

@@ -260,6 +260,7 @@ attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         idx -= tiles_r;
     }
     if (r >= requests) return;
+    idx = tiles_r - 1 - idx;                         // a request's last tiles have the most keys: they start first
     const int g = blockIdx.y;
     const int t0 = idx * tok, n_rows = row_count[r], a0 = row_start[r], hist = history[r];
     const int n_tok = min(tok, n_rows - t0);

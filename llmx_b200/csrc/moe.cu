@@ -248,18 +248,22 @@ moe_tc_kernel(const __nv_bfloat16* __restrict__ a, int a_div, const __nv_bfloat1
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(af[h][0]), "=r"(af[h][1]), "=r"(af[h][2]), "=r"(af[h][3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
             }
+            // All of the step's fragments are asked for before the first product, so that the reads overlap the products
+            // of the step before (the statements keep their order; a warp's products do not wait for one another).
+            uint32_t b[4][4];
 #pragma unroll
             for (int t2 = 0; t2 < 4; ++t2) {
-                uint32_t b[4];
                 const __nv_bfloat16* p = bs + (size_t)(64 * wn + 16 * t2 + b_row) * TC_LD + ks + b_k;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+                             : "=r"(b[t2][0]), "=r"(b[t2][1]), "=r"(b[t2][2]), "=r"(b[t2][3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+            }
+#pragma unroll
+            for (int t2 = 0; t2 < 4; ++t2)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    mma_bf16(acc[h][2 * t2], af[h], b[0], b[1]);
-                    mma_bf16(acc[h][2 * t2 + 1], af[h], b[2], b[3]);
+                    mma_bf16(acc[h][2 * t2], af[h], b[t2][0], b[t2][1]);
+                    mma_bf16(acc[h][2 * t2 + 1], af[h], b[t2][2], b[t2][3]);
                 }
-            }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");

@@ -119,8 +119,8 @@ class Model:
                     raise ValueError(f"layer order step {n}: block {s.block} has no cache but an entry is named")
                 continue
             if len(entries) != len(specs):
-                raise ValueError(f"layer order step {n}: block {s.block} needs {len(specs)} cache "
-                                 f"{'entry' if len(specs) == 1 else 'entries'}" + (f", {len(entries)} named" if entries else ""))
+                need = "a cache entry" if len(specs) == 1 else f"{len(specs)} cache entries"
+                raise ValueError(f"layer order step {n}: block {s.block} needs {need}" + (f", {len(entries)} named" if entries else ""))
             for e in entries:
                 named.add(e)
                 if s.write_cache:

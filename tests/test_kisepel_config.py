@@ -192,3 +192,20 @@ def test_plain_experts_follow_the_table_and_loop_order():
     assert np.allclose(out[1], 0.5 * (plain.gated_unit(h[1:], w, "m.e1.") + plain.gated_unit(h[1:], w, "m.e2."))[0])
     assert plain.layer_runs(CFG) == [(0, False), (1, False), (2, False), (1, True), (2, False), (1, True), (2, False), (3, False)]
     assert plain.layer_runs({"layers": [0, 0, 0]}) == [(0, False), (1, False), (2, False)]
+
+
+def test_layer_order_with_several_entries_a_step_is_checked():
+    from llmx_b200.models import LayerStep, Model
+    from llmx_b200.registry import architecture_of
+    entry = architecture_of(CFG)
+    m = entry.build(entry.config_cls.from_dict(CFG))
+    kw = dict(embedding=m.embedding, blocks=m.blocks, head=m.head, vocab_size=130, max_positions=64)
+    with pytest.raises(ValueError, match="needs 2 cache entries, 1 named"):
+        Model(order=[LayerStep(2, 0)], **kw)
+    with pytest.raises(ValueError, match="needs a cache entry, 2 named"):
+        Model(order=[LayerStep(0, (0, 1))], **kw)
+    with pytest.raises(ValueError, match="both write"):
+        Model(order=[LayerStep(2, (0, 1)), LayerStep(0, 1)], **kw)
+    ok = Model(order=[LayerStep(2, (1, 0)), LayerStep(2, (3, 2), add_embedding=True)], **kw)
+    assert [type(s).__name__ for s in ok.cache_entry_specs()] == ["StateSpec", "KVSpec", "StateSpec", "KVSpec"]
+    assert ok.native is None

@@ -17,7 +17,7 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAX_PER_LANE = 8;  // head widths up to 256
+constexpr int MAX_PER_LANE = 16;  // key and value widths up to 512
 
 template <typename QT, typename KVT>
 __global__ void __launch_bounds__(128)

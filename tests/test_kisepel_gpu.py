@@ -155,6 +155,7 @@ ONE_LAYER = {
                                                             r_dim=36, r_vdim=4, conv=1, decay_rank=1, gate_rank=2, mlp=None),
     "parallel_chunk_of_one": parallel(heads=2, kv_heads=2, dim=8, vdim=8, chunk=1, rot_dims=4, mlp=None),
     "parallel_wide_heads": parallel(heads=2, kv_heads=1, dim=160, vdim=72, chunk=50, rot_dims=64, r_heads=2, r_kv_heads=1, r_dim=136, r_vdim=6, mlp=None),
+    "parallel_heads_wider_than_256": parallel(heads=2, kv_heads=1, dim=320, vdim=272, chunk=40, rot_dims=32, r_heads=2, r_kv_heads=1, r_dim=16, r_vdim=8, mlp=None),
     "experts_one_of_many": lightning(mlp=moe(9, 1, 20, None)),
     "experts_all_of_them_with_shared": lightning(mlp=moe(3, 3, 50, 10)),
     "experts_wide": lightning(mlp=moe(4, 2, 136, 72)),
